@@ -171,8 +171,10 @@ class TorchOps:
             state[slot] = s
         return out.to(out_dtype)
 
-    def moe_route(self, x, w_router, correction, *, n_experts, top, scale, renormalize, shared_gate):
+    def moe_route(self, x, w_router, correction, *, n_experts, top, scale, renormalize, shared_gate, logit_bias=None):
         z = x.float() @ w_router.t()
+        if logit_bias is not None:
+            z[:, :n_experts] += logit_bias
         s = torch.softmax(z[:, :n_experts], dim=-1)
         choice = s if correction is None else s + correction
         chosen = torch.topk(choice, top, dim=-1).indices
@@ -182,15 +184,20 @@ class TorchOps:
         gate = torch.sigmoid(z[:, n_experts]).contiguous() if shared_gate else None
         return chosen.to(torch.int32).contiguous(), (w * np.float32(scale)).contiguous(), gate
 
-    def moe_experts(self, x, chosen, weights, w_up, w_down, *, activation, shared=None, shared_gate=None):
-        """w_up [E, hidden, dim]; w_down [dim, >= E * hidden], expert e's matrix in columns e * hidden ..."""
+    def moe_experts(self, x, chosen, weights, w_up, w_down, *, activation, shared=None, shared_gate=None, gated=False):
+        """w_up [E, hidden, dim] (gated: [E, 2 * hidden, dim], rows [gate; up]); w_down [dim, >= E * hidden], expert e's
+        matrix in columns e * hidden ..."""
         T, top = chosen.shape
-        hidden = w_up.shape[1]
+        hidden = w_up.shape[1] // (2 if gated else 1)
         out = torch.zeros((T, w_down.shape[0]), dtype=torch.float32, device=x.device)
         for k in range(top):
             for e in chosen[:, k].unique().tolist():
                 rows = (chosen[:, k] == e).nonzero().flatten()
-                u = self._act(x[rows].float() @ w_up[e].float().t(), activation).to(x.dtype)
+                u = x[rows].float() @ w_up[e].float().t()
+                if gated:
+                    u = (self._act(u[:, :hidden].to(x.dtype).float(), activation) * u[:, hidden:].to(x.dtype).float()).to(x.dtype)
+                else:
+                    u = self._act(u, activation).to(x.dtype)
                 y = (u.float() @ w_down[:, e * hidden:(e + 1) * hidden].float().t()).to(x.dtype)
                 out[rows] += weights[rows, k:k + 1] * y.float()
         if shared is not None:
@@ -228,7 +235,7 @@ class TorchOps:
                         up_offset=up_offset)
 
     def project_and_store(self, proj, *, n_q, n_k, n_v, n_extra, bias, q_norm, k_norm, eps, k_pages, v_pages,
-                          slot_mapping, page_size, out_dtype):
+                          slot_mapping, page_size, out_dtype, norm_head_dim=None):
         """A row of proj is [q | k | v | extra].  Bias added, q and k each normalised over their whole
         width (where a weight is given), k and v written to their pages, sigmoid of the extra columns."""
         x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
@@ -236,10 +243,17 @@ class TorchOps:
         if bias is not None:
             x = x + bias
         q, k, v, e = x.split([n_q, n_k, n_v, n_extra], dim=1)
-        if q_norm is not None:
-            q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm
-        if k_norm is not None and n_k:
-            k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm
+        if norm_head_dim:            # every head by itself, one weight for all heads
+            def per_head(y, w):
+                y = y.unflatten(1, (-1, norm_head_dim))
+                return (y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps) * w).flatten(1)
+            q = per_head(q, q_norm) if q_norm is not None else q
+            k = per_head(k, k_norm) if k_norm is not None and n_k else k
+        else:
+            if q_norm is not None:
+                q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm
+            if k_norm is not None and n_k:
+                k = k * torch.rsqrt(k.pow(2).mean(-1, keepdim=True) + eps) * k_norm
         if k_pages is not None and n_k:
             sm = slot_mapping.long()
             page, slot = sm // page_size, sm % page_size
@@ -247,6 +261,101 @@ class TorchOps:
             if v_pages is not None and n_v:
                 v_pages[page, :, slot] = v.reshape(v.shape[0], v_pages.shape[1], v_pages.shape[3]).to(v_pages.dtype)
         return q.to(out_dtype).contiguous(), (torch.sigmoid(e).to(out_dtype).contiguous() if n_extra else None)
+
+    # ---- sums, short convolutions and recurrences with a matrix state
+    def stream_add(self, h, *, normed, coef, eps, plain, out_dtype):
+        """h += coef * sum_i t_i / sqrt(mean(t_i^2) + eps) * w_i + sum_j p_j (in place, float32); the new rows in out_dtype."""
+        for t, w in normed:
+            t = t.float()
+            h += np.float32(coef) * (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w)
+        for p in plain:
+            h += p.float().sum(0) if p.dim() == 3 else p.float()
+        return self.stream_rows(h, out_dtype)
+
+    def short_conv(self, x, w, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, activation, residual, out_dtype):
+        """Causal convolution over time per channel: out_t = sum_j w[:, j] x_(t - taps + 1 + j) (+ x_t with residual),
+        then the activation.  state [slots, taps - 1, C] holds every request's last inputs (zeros for a fresh one)."""
+        C, taps = w.shape
+        xf = x.float()
+        out = torch.empty((x.shape[0], C), dtype=torch.float32, device=x.device)
+        qs = q_start.tolist()
+        for b in range(n_seqs):
+            slot = int(state_slot[b])
+            rows = xf[qs[b]:qs[b + 1]]
+            if taps > 1:
+                before = torch.zeros((taps - 1, C)) if int(fresh[b]) else state[slot].clone()
+                full = torch.cat([before, rows])
+                state[slot] = full[-(taps - 1):]
+            else:
+                full = rows
+            y = sum(full[j:j + rows.shape[0]] * w[:, j] for j in range(taps))
+            out[qs[b]:qs[b + 1]] = y + rows if residual else y
+        if activation is not None:
+            out = self._act(out, activation)
+        return out.to(out_dtype)
+
+    def recurrence_prep(self, x, *, scale, n_heads, head_dim, positions=None, table=None, rot_dims=0, unit_eps=None):
+        """float32 [T, n_heads * head_dim]: rotated by position on the first rot_dims coordinates of every head
+        (coordinate i with i + rot_dims / 2), or made unit vectors per head; then times scale."""
+        y = x.float().unflatten(1, (n_heads, head_dim)).clone()
+        if table is not None and rot_dims:
+            half = rot_dims // 2
+            cs = table[positions.long()][:, None, :half]
+            a, b = y[..., :half].clone(), y[..., half:rot_dims].clone()
+            y[..., :half] = a * cs[..., 0] - b * cs[..., 1]
+            y[..., half:rot_dims] = b * cs[..., 0] + a * cs[..., 1]
+        if unit_eps is not None:
+            y = y * torch.rsqrt(y.pow(2).sum(-1, keepdim=True) + unit_eps)
+        return (y * np.float32(scale)).flatten(1).contiguous()
+
+    def linear_recurrence(self, q, k, v, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, decay=None,
+                          beta_logits=None, decay_logits=None, decay_rate=None, decay_bias=None):
+        """state [slots, H, dk, dv] float32; q, k float32 [T, G * dk] (G heads shared by H / G value heads each), v [T, H * dv].
+        decay: S = decay_h S + k v^T.  Otherwise the gated delta rule: S = g S; u = beta (v - S^T k); S += k u^T.  o = S^T q."""
+        H, dk, dv = state.shape[1:]
+        G = q.shape[1] // dk
+        T = q.shape[0]
+        qh, kh = q.view(T, G, dk).float(), k.view(T, G, dk).float()
+        vh = v.float().reshape(T, H, dv)
+        if decay is None:
+            beta = torch.sigmoid(beta_logits.float())
+            g = torch.exp(-decay_rate * torch.nn.functional.softplus(decay_logits.float() + decay_bias))
+        out = torch.empty((T, H, dv), dtype=torch.float32, device=q.device)
+        qs = q_start.tolist()
+        for b in range(n_seqs):
+            slot = int(state_slot[b])
+            S = torch.zeros((H, dk, dv)) if int(fresh[b]) else state[slot].clone()
+            for t in range(qs[b], qs[b + 1]):
+                kt = kh[t].repeat_interleave(H // G, dim=0)
+                qt = qh[t].repeat_interleave(H // G, dim=0)
+                if decay is not None:
+                    S = decay[:, None, None] * S + kt[:, :, None] * vh[t][:, None, :]
+                else:
+                    S = g[t][:, None, None] * S
+                    u = beta[t][:, None] * (vh[t] - torch.einsum("hkv,hk->hv", S, kt))
+                    S = S + kt[:, :, None] * u[:, None, :]
+                out[t] = torch.einsum("hkv,hk->hv", S, qt)
+            state[slot] = S
+        return out.flatten(1)
+
+    def head_norm_gate(self, o, gate, weight, eps, *, head_dim, out_dtype):
+        """Every head of o (float32 [T, H * head_dim]) divided by its root mean square, times the weight (if any), times silu(gate)."""
+        y = o.float().unflatten(1, (-1, head_dim))
+        y = y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+        if weight is not None:
+            y = y * weight
+        g = gate.float()
+        return (y.flatten(1) * g * torch.sigmoid(g)).to(out_dtype)
+
+    def side_gate(self, u, token_ids, table, out_dtype):
+        """gelu_tanh(u) * table[token]."""
+        return (self._act(u.float(), "gelu_tanh") * table[token_ids.long()].float()).to(out_dtype)
+
+    def polynorm(self, z, coef, eps, out_dtype):
+        """a N(z) + b N(z^2) + c N(z^3) + e with N(y) = y / sqrt(mean(y^2) + eps) over a row; coef = (a, b, c, e)."""
+        z = z.float().sum(0) if z.dim() == 3 else z.float()
+        n = lambda y: y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
+        return (coef[0] * n(z) + coef[1] * n(z * z) + coef[2] * n(z * z * z) + coef[3]).to(out_dtype)
 
     def head_linear(self, x, w):
         """x [T, H, K] against w [H, N, K]: out[t, h] = w[h] @ x[t, h]."""

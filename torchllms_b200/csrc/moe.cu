@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ x
 
 // From the logits to the choice: a warp per token.  Shared memory per warp: scores, then what the choice looks at.
 __global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
-                                                         int* __restrict__ chosen, float* __restrict__ weights,
+                                                         const float* __restrict__ logit_bias, int* __restrict__ chosen, float* __restrict__ weights,
                                                          float* __restrict__ gate, int n_tokens, int n_experts, int n_rows,
                                                          int top, float scale, int renormalize) {
     extern __shared__ float sm[];
@@ -80,14 +80,19 @@ __global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict
     float* ch = sc + n_experts;
     const float* z = logits + (size_t)t * n_rows;
     float mx = -INFINITY;
-    for (int e = lane; e < n_experts; e += 32) mx = fmaxf(mx, z[e]);
+    // (the logits with their bias pass through ch[] on the way to the scores)
+    for (int e = lane; e < n_experts; e += 32) {
+        const float v = z[e] + (logit_bias != nullptr ? logit_bias[e] : 0.f);
+        ch[e] = v;
+        mx = fmaxf(mx, v);
+    }
     mx = warp_max(mx);
     float sum = 0.f;
-    for (int e = lane; e < n_experts; e += 32) sum += expf(z[e] - mx);
+    for (int e = lane; e < n_experts; e += 32) sum += expf(ch[e] - mx);
     sum = warp_sum(sum);
     const float inv = 1.f / sum;
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = expf(z[e] - mx) * inv;
+        const float s = expf(ch[e] - mx) * inv;
         sc[e] = s;
         ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
     }
@@ -402,17 +407,17 @@ extern "C" int tl_moe_logits(const void* x, int dtype, const float* w_router, fl
 }
 
 // logits: float32 [n_tokens][n_rows], n_rows = n_experts (+ 1 with gate != null: the shared expert's gate);
-// correction: float32 [n_experts] or null; chosen: int32 [n_tokens][top]; weights: float32 [n_tokens][top];
+// correction, logit_bias (added to the logits before anything else): float32 [n_experts] or null; chosen: int32 [n_tokens][top]; weights: float32 [n_tokens][top];
 // gate: float32 [n_tokens] or null.
-extern "C" int tl_moe_select(const float* logits, const float* correction, int* chosen, float* weights, float* gate,
-                             int n_tokens, int n_experts, int top, float scale, int renormalize, void* stream) {
+extern "C" int tl_moe_select(const float* logits, const float* correction, const float* logit_bias, int* chosen, float* weights,
+                             float* gate, int n_tokens, int n_experts, int top, float scale, int renormalize, void* stream) {
     if (n_tokens <= 0) return TL_OK;
     if (n_experts <= 0 || top <= 0 || top > n_experts) return TL_BAD_SIZE;
     const int n_rows = n_experts + (gate != nullptr ? 1 : 0);
     const size_t smem = (size_t)4 * 2 * n_experts * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
     return (int)tl_launch(moe_select_kernel, dim3((n_tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, logits, correction,
-                          chosen, weights, gate, n_tokens, n_experts, n_rows, top, scale, renormalize);
+                          logit_bias, chosen, weights, gate, n_tokens, n_experts, n_rows, top, scale, renormalize);
 }
 
 // rows of a tile for this many (token, choice) pairs, and how many tiles there can be at most

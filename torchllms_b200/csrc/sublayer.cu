@@ -128,7 +128,23 @@ struct ProjectParams {
     void* v_pages;          // [pages, kv_heads, page_size, v_dim] or null
     const int* slot_mapping;
     int page_size, n_kv_heads, k_dim, v_dim;
+    int norm_head;          // > 0: q and k are normed head by head, heads of this size, the weights [norm_head] shared by all heads
 };
+
+// the scale of every head of q and k (shared memory behind the row: (n_q + n_k) / norm_head floats), a warp per head
+__device__ __forceinline__ void head_scales(const ProjectParams& p, const float* row, float* scales) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    const int heads = (p.n_q + p.n_k) / p.norm_head;
+    for (int h = warp; h < heads; h += n_warps) {
+        float ssq = 0.f;
+        for (int d = lane; d < p.norm_head; d += 32) {
+            const float v = row[h * p.norm_head + d];
+            ssq = fmaf(v, v, ssq);
+        }
+        ssq = warp_sum(ssq);
+        if (lane == 0) scales[h] = rsqrtf(ssq / (float)p.norm_head + p.eps);
+    }
+}
 
 // One CTA per token; the row in shared memory as float32.
 template <typename TI, typename TO>
@@ -153,10 +169,19 @@ __global__ void project_store_kernel(const ProjectParams p) {
     if (p.q_norm != nullptr) rq = rsqrtf(block_sum(ssq_q, part) / (float)p.n_q + p.eps);
     if (p.k_norm != nullptr && p.n_k > 0) rk = rsqrtf(block_sum(ssq_k, part) / (float)p.n_k + p.eps);
     __syncthreads();
+    const int nh = p.norm_head;
+    const float* hs = row + width;
+    if (nh > 0) {
+        head_scales(p, row, row + width);
+        __syncthreads();
+    }
 
     TO* q_out = reinterpret_cast<TO*>(p.q_out) + (size_t)t * p.n_q;
-    for (int c = threadIdx.x; c < p.n_q; c += blockDim.x)
-        q_out[c] = from_float<TO>(p.q_norm != nullptr ? row[c] * rq * p.q_norm[c] : row[c]);
+    for (int c = threadIdx.x; c < p.n_q; c += blockDim.x) {
+        float v = row[c];
+        if (p.q_norm != nullptr) v *= nh > 0 ? hs[c / nh] * p.q_norm[c % nh] : rq * p.q_norm[c];
+        q_out[c] = from_float<TO>(v);
+    }
 
     if (p.k_pages != nullptr && p.n_k > 0) {
         const int slot = p.slot_mapping[t];
@@ -166,7 +191,8 @@ __global__ void project_store_kernel(const ProjectParams p) {
             const float* k = row + p.n_q;
             for (int c = threadIdx.x; c < p.n_k; c += blockDim.x) {
                 const int head = c / p.k_dim, d = c - head * p.k_dim;
-                const float v = p.k_norm != nullptr ? k[c] * rk * p.k_norm[c] : k[c];
+                float v = k[c];
+                if (p.k_norm != nullptr) v *= nh > 0 ? hs[(p.n_q + c) / nh] * p.k_norm[c % nh] : rk * p.k_norm[c];
                 kp[((page * p.n_kv_heads + head) * p.page_size + off) * p.k_dim + d] = from_float<TO>(v);
             }
             if (p.v_pages != nullptr && p.n_v > 0) {
@@ -290,12 +316,19 @@ __global__ void project_store_vec_kernel(const ProjectParams p) {
     if (p.q_norm != nullptr) rq = rsqrtf(block_sum(ssq_q, part) / (float)p.n_q + p.eps);
     if (p.k_norm != nullptr && p.n_k > 0) rk = rsqrtf(block_sum(ssq_k, part) / (float)p.n_k + p.eps);
     __syncthreads();
+    const int nh = p.norm_head;
+    const float* hs = row + width;
+    if (nh > 0) {
+        head_scales(p, row, row + width);
+        __syncthreads();
+    }
 
     TO* q_out = reinterpret_cast<TO*>(p.q_out) + (size_t)t * p.n_q;
     for (int c = threadIdx.x * 4; c < p.n_q; c += blockDim.x * 4) {
         float4 v = ld4(row + c);
         if (p.q_norm != nullptr) {
-            const float4 w = ld4(p.q_norm + c);
+            const float4 w = ld4(p.q_norm + (nh > 0 ? c % nh : c));
+            if (nh > 0) rq = hs[c / nh];
             v.x *= rq * w.x; v.y *= rq * w.y; v.z *= rq * w.z; v.w *= rq * w.w;
         }
         st4(q_out + c, v);
@@ -310,7 +343,8 @@ __global__ void project_store_vec_kernel(const ProjectParams p) {
                 const int head = c / p.k_dim, d = c - head * p.k_dim;
                 float4 v = ld4(k + c);
                 if (p.k_norm != nullptr) {
-                    const float4 w = ld4(p.k_norm + c);
+                    const float4 w = ld4(p.k_norm + (nh > 0 ? c % nh : c));
+                    if (nh > 0) rk = hs[(p.n_q + c) / nh];
                     v.x *= rk * w.x; v.y *= rk * w.y; v.z *= rk * w.z; v.w *= rk * w.w;
                 }
                 st4(kp + ((page * p.n_kv_heads + head) * p.page_size + off) * p.k_dim + d, v);
@@ -455,7 +489,7 @@ extern "C" int tl_project_store(const void* proj, int in_dtype, int splits, long
                                 const float* q_norm, const float* k_norm, float eps, int n_q, int n_k, int n_v,
                                 int n_extra, void* q_out, void* extra_out, int out_dtype, void* k_pages, void* v_pages,
                                 const int* slot_mapping, int page_size, int n_kv_heads, int k_dim, int v_dim,
-                                int n_tokens, void* stream) {
+                                int n_tokens, int norm_head, void* stream) {
     if (n_tokens <= 0) return TL_OK;
     if (n_q < 0 || n_k < 0 || n_v < 0 || n_extra < 0 || splits < 1) return TL_BAD_SIZE;
     const int width = n_q + n_k + n_v + n_extra;
@@ -464,16 +498,18 @@ extern "C" int tl_project_store(const void* proj, int in_dtype, int splits, long
         (slot_mapping == nullptr || page_size <= 0 || n_kv_heads <= 0 || k_dim <= 0 || n_k != n_kv_heads * k_dim))
         return TL_BAD_SIZE;
     if (k_pages != nullptr && v_pages != nullptr && n_v > 0 && (v_dim <= 0 || n_v != n_kv_heads * v_dim)) return TL_BAD_SIZE;
-    const size_t smem = (size_t)width * sizeof(float);
+    if (norm_head < 0 || (norm_head > 0 && (n_q % norm_head != 0 || n_k % norm_head != 0))) return TL_BAD_SIZE;
+    const size_t smem = (size_t)(width + (norm_head > 0 ? (n_q + n_k) / norm_head : 0)) * sizeof(float);
     if (smem > 200 * 1024) return TL_TOO_LARGE;
     ProjectParams p;
+    p.norm_head = norm_head;
     p.proj = proj; p.splits = splits; p.plane = plane; p.bias = bias; p.q_norm = q_norm; p.k_norm = k_norm; p.eps = eps;
     p.n_q = n_q; p.n_k = n_k; p.n_v = n_v; p.n_extra = n_extra; p.q_out = q_out; p.extra_out = extra_out;
     p.k_pages = k_pages; p.v_pages = v_pages; p.slot_mapping = slot_mapping; p.page_size = page_size;
     p.n_kv_heads = n_kv_heads; p.k_dim = k_dim; p.v_dim = v_dim;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    const bool vec = n_q % 4 == 0 && n_k % 4 == 0 && n_v % 4 == 0 && n_extra % 4 == 0 && plane % 4 == 0 &&
+    const bool vec = n_q % 4 == 0 && n_k % 4 == 0 && n_v % 4 == 0 && n_extra % 4 == 0 && plane % 4 == 0 && norm_head % 4 == 0 &&
                      (k_pages == nullptr || n_k == 0 || (k_dim % 4 == 0 && aligned16(k_pages))) &&
                      (v_pages == nullptr || n_v == 0 || (v_dim % 4 == 0 && aligned16(v_pages))) && aligned16(proj) &&
                      aligned16(q_out) && (extra_out == nullptr || aligned16(extra_out)) && (bias == nullptr || aligned16(bias)) &&

@@ -14,7 +14,7 @@ from typing import Dict, List, Mapping, Optional, Sequence, Tuple
 
 import torch
 
-from ..parts import attention, block, ffn, latent_attention, moe, norm, recurrent, rope  # noqa: F401  (register the built-in parts)
+from ..parts import attention, block, ffn, latent_attention, moe, norm, pair, recurrent, rope  # noqa: F401  (register the built-in parts)
 from ..parts.base import BLOCKS, NORMS, BuildEnv, CacheNeed, Residual, StateNeed, as_compute
 from ..parts.spec import ModelSpec
 from ..weights.loader import ExpectedTensor
@@ -36,6 +36,7 @@ class Model:
                             max_positions=self.max_positions, ops=ops)
         self.blocks = [BLOCKS.build(layer.block, self.env) for layer in spec.layers]
         self.final_norm = NORMS.build(spec.final_norm, self.env)
+        self.embedding_norm = None if spec.embedding_norm is None else NORMS.build(spec.embedding_norm, self.env)
         self.graph_safe = self.final_norm.graph_safe and all(b.graph_safe for b in self.blocks)
         self.embedding: Optional[torch.Tensor] = None
         self.position_table: Optional[torch.Tensor] = None
@@ -52,6 +53,9 @@ class Model:
                 out[f"{layer.name}.{name}"] = e
         for name, e in self.final_norm.expected_tensors().items():
             out[f"{spec.final_norm_prefix}.{name}"] = e
+        if self.embedding_norm is not None:
+            for name, e in self.embedding_norm.expected_tensors().items():
+                out[f"{spec.embedding_norm_prefix}.{name}"] = e
         if not spec.tie_head:
             out[spec.head_tensor] = ExpectedTensor((spec.vocab_size, spec.dim))
         return out
@@ -66,6 +70,9 @@ class Model:
             blk.load({name: tensors[f"{layer.name}.{name}"] for name in blk.expected_tensors()})
         self.final_norm.load({name: tensors[f"{spec.final_norm_prefix}.{name}"]
                               for name in self.final_norm.expected_tensors()})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({name: tensors[f"{spec.embedding_norm_prefix}.{name}"]
+                                      for name in self.embedding_norm.expected_tensors()})
         self.head = self.embedding if spec.tie_head else as_compute(tensors[spec.head_tensor], self.env)
 
     def weight_bytes(self) -> int:
@@ -117,6 +124,12 @@ class Model:
         else:
             residual = Residual(self.ops.embed(ctx.token_ids, self.embedding, scale=self.spec.embedding_scale,
                                                positions=ctx.positions, position_table=self.position_table))
+        if self.embedding_norm is not None:
+            # the stream is the norm of the table's rows, taken in 32-bit and kept so
+            if residual.history is not None:
+                raise RuntimeError("a normed embedding and a kept history are not built together")
+            residual = Residual(self.ops.rmsnorm(residual.h, None, self.embedding_norm.weight, self.embedding_norm.eps,
+                                                 out_dtype=torch.float32))
         order = self.spec.run_order
         for i, run in enumerate(order):
             residual.next_norm = self.blocks[order[i + 1].layer].input_norm if i + 1 < len(order) else None
@@ -126,4 +139,5 @@ class Model:
         if ctx.n_want == 0:
             return None
         x = self.final_norm.forward(residual, rows=ctx.want_rows)
-        return self.ops.linear(x, self.head, out_dtype=torch.float32)
+        logits = self.ops.linear(x, self.head, out_dtype=torch.float32)
+        return logits if self.spec.logit_scale == 1.0 else logits.mul_(self.spec.logit_scale)

@@ -16,6 +16,11 @@ knowing of each other.
     kernels that end a chain of products (rotary encoding, the SwiGLU gate) apply the scale, in
     float32, where they convert to the activation dtype anyway.
 
+:class:`NormedSum`
+    A mixer's result that is a weighted sum of RMS-normed tensors, not yet taken:
+    ``coef * sum_i t_i / sqrt(mean(t_i^2) + eps) * w_i``.  A block that adds the result to the
+    stream hands the terms to the kernel that takes the sum, so the norms run in 32-bit inside it.
+
 The reference computes ``norm(x) @ W`` (torchllms/models/networks.py:195-200, :635-644); here
 the same number is ``(x * w_norm) @ W * rsqrt(mean(x^2) + eps)``, which lets the kernel that
 produces ``x`` finish without a pass over the whole row.
@@ -61,3 +66,17 @@ class RowScaled:
         """The rows themselves, in ``dtype`` (plain PyTorch; no kernel of the package is involved)."""
         x = self.x.float().sum(0) if self.x.dim() == 3 else self.x.float()
         return (x * self.scale()[:, None]).to(dtype)
+
+
+@dataclass
+class NormedSum:
+    terms: tuple             # ((tensor [T, dim], weight float32 [dim]), ...)
+    coef: float
+    eps: float
+
+    def take(self, ops, out_dtype: torch.dtype):
+        """The sum as a tensor (a kernel of its own: the sum onto a stream of zeros)."""
+        t = self.terms[0][0]
+        h = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+        out = ops.stream_add(h, normed=self.terms, coef=self.coef, eps=self.eps, plain=(), out_dtype=out_dtype)
+        return out

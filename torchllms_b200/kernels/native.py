@@ -151,7 +151,7 @@ class NativeOps:
     # ------------------------------------------------------------ libraries
     def prepare(self, dtype: torch.dtype, sampling: bool = True) -> None:
         """Compile, side by side, what a model of this dtype will call."""
-        names = ["elementwise", "sublayer", "rope", "attention", "gemm_simt", "recurrent", "moe"]
+        names = ["elementwise", "sublayer", "rope", "attention", "gemm_simt", "recurrent", "moe", "matrix_state", "stream_sum"]
         if dtype == torch.bfloat16:
             names += ["attention_mma", "attention_decode", "gemm_tcgen05"]
         if sampling:
@@ -379,12 +379,15 @@ class NativeOps:
     def project_and_store(self, proj: torch.Tensor, *, n_q: int, n_k: int, n_v: int, n_extra: int,
                           bias: Optional[torch.Tensor], q_norm: Optional[torch.Tensor], k_norm: Optional[torch.Tensor],
                           eps: float, k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor],
-                          slot_mapping: Optional[torch.Tensor], page_size: int, out_dtype: torch.dtype):
+                          slot_mapping: Optional[torch.Tensor], page_size: int, out_dtype: torch.dtype,
+                          norm_head_dim: Optional[int] = None):
         """What follows a mixer's stacked input projection, whose rows are ``[q | k | v | extra]``
         (``proj`` is ``[T, width]`` or float32 partial sums ``[splits, T, width]``): the bias is
         added, q and k are each RMS-normed over their whole width where a weight is given, k and v
         go into their pages at ``slot_mapping`` (``k_pages`` ``[pages, kv_heads, page_size, k_dim]``,
-        ``v_pages`` likewise or ``None``), and ``q`` and ``sigmoid(extra)`` come back in ``out_dtype``."""
+        ``v_pages`` likewise or ``None``), and ``q`` and ``sigmoid(extra)`` come back in ``out_dtype``.
+        With ``norm_head_dim`` q and k are normed head by head (heads of that size) and the weights,
+        ``norm_head_dim`` numbers each, are shared by all heads."""
         _cuda_contig(proj, "projection")
         width = n_q + n_k + n_v + n_extra
         _need(proj.dim() in (2, 3) and proj.shape[-1] == width and proj.dtype in _DT, "projection rows must be [q | k | v | extra]")
@@ -393,7 +396,9 @@ class NativeOps:
         _need(out_dtype in _DT and (out_dtype == proj.dtype or proj.dtype == torch.float32), "project_and_store cannot widen bfloat16 input")
         _need(width * 4 <= 200 * 1024, f"project_and_store keeps a row in shared memory: {width} columns exceed 51200")
         T = proj.shape[-2]
-        for t, n, name in ((bias, width, "bias"), (q_norm, n_q, "q_norm"), (k_norm, n_k, "k_norm")):
+        nh = int(norm_head_dim or 0)
+        _need(nh == 0 or (n_q % nh == 0 and n_k % nh == 0), "q and k must be whole heads of norm_head_dim")
+        for t, n, name in ((bias, width, "bias"), (q_norm, nh or n_q, "q_norm"), (k_norm, nh or n_k, "k_norm")):
             if t is not None:
                 _cuda_contig(t, name, torch.float32)
                 _need(t.numel() == n, f"{name} must have {n} elements")
@@ -419,7 +424,7 @@ class NativeOps:
             _ptr(proj), _DT[proj.dtype], splits, ctypes.c_longlong(proj.stride(0) if splits > 1 else 0), _ptr(bias),
             _ptr(q_norm), _ptr(k_norm), ctypes.c_float(eps), n_q, n_k, n_v, n_extra, _ptr(q), _ptr(extra), _DT[out_dtype],
             _ptr(k_pages), _ptr(v_pages), _ptr(slot_mapping if k_pages is not None else None), page_size, kvh, kd, vd, T,
-            _stream())
+            nh, _stream())
         _check(rc, "project_store")
         self.launches += 1
         return q, extra
@@ -643,13 +648,217 @@ class NativeOps:
         self.launches += 3 if max_q_len > 8 else 1
         return out
 
+    # ------------------------------------------------- matrix states, short convolutions, sums of sublayers
+    @staticmethod
+    def _rows_view(t: torch.Tensor, name: str):
+        """A ``[T, n]`` tensor whose rows may be a column range of a wider row: the pitch in elements."""
+        _need(t.is_cuda and t.dim() == 2 and t.dtype in _DT and (t.shape[1] == 0 or t.stride(1) == 1),
+              f"{name} must be [tokens, columns] on the GPU with columns side by side, float32 or bfloat16")
+        return ctypes.c_longlong(t.stride(0))
+
+    @staticmethod
+    def _state_view(state: torch.Tensor, inner: int, name: str):
+        """Per-request state ``[slots, ...]`` that may be a field of a wider row: the slots' pitch in elements."""
+        _need(state.is_cuda and state.dtype == torch.float32 and state[0].is_contiguous() and state[0].numel() == inner,
+              f"{name} must be float32 [slots, ...] on the GPU, every slot's part contiguous")
+        return ctypes.c_longlong(state.stride(0))
+
+    def _seq_index(self, q_start, state_slot, fresh, n_seqs):
+        for t, name in ((q_start, "q_start"), (state_slot, "state_slot"), (fresh, "fresh")):
+            _cuda_contig(t, name, torch.int32)
+        _need(q_start.numel() >= n_seqs + 1 and state_slot.numel() >= n_seqs and fresh.numel() >= n_seqs,
+              "q_start, state_slot and fresh must cover every request of the step")
+
+    @_timed
+    def short_conv(self, x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], q_start: torch.Tensor,
+                   state_slot: torch.Tensor, fresh: torch.Tensor, *, n_seqs: int, max_q_len: int, activation: Optional[str],
+                   residual: bool, out_dtype: torch.dtype) -> torch.Tensor:
+        """Causal convolution over time on every channel: ``out_t = sum_j w[:, j] x_(t - taps + 1 + j)`` (plus ``x_t``
+        with ``residual``), then ``silu`` if asked for.  ``x`` is ``[T, C]`` (a column range of a wider row will do),
+        ``w`` float32 ``[C, taps]``; ``state`` (float32 ``[slots, taps - 1, C]``, ``None`` with one tap) holds every
+        request's last inputs: read (zeros where ``fresh``) and left as the portion leaves them."""
+        ldx = self._rows_view(x, "convolution input")
+        _cuda_contig(w, "convolution taps", torch.float32)
+        C, taps = w.shape
+        _need(x.shape[1] == C and 1 <= taps <= 8, "short_conv: x [T, C] against w [C, taps], at most 8 taps")
+        _need(activation in (None, "silu"), f"short_conv knows no activation {activation!r}")
+        _need(out_dtype in _DT and (out_dtype == x.dtype or x.dtype == torch.float32), "short_conv cannot widen bfloat16 input")
+        self._seq_index(q_start, state_slot, fresh, n_seqs)
+        pitch = ctypes.c_longlong(0)
+        if taps > 1:
+            _need(state is not None, "a convolution of several taps keeps state")
+            pitch = self._state_view(state, (taps - 1) * C, "convolution state")
+        T = x.shape[0]
+        out = torch.empty((T, C), dtype=out_dtype, device=x.device)
+        rc = self._lib("matrix_state").tl_short_conv(
+            _ptr(x), _DT[x.dtype], ldx, _ptr(w), _ptr(state if taps > 1 else None), pitch, _ptr(q_start), _ptr(state_slot),
+            _ptr(fresh), _ptr(out), _DT[out_dtype], T, n_seqs, C, taps, max_q_len, 1 if activation == "silu" else 0,
+            1 if residual else 0, _stream())
+        _check(rc, "short_conv")
+        self.launches += 2 if (max_q_len > 8 and taps > 1) else 1
+        return out
+
+    @_timed
+    def recurrence_prep(self, x: torch.Tensor, *, scale: float, n_heads: int, head_dim: int,
+                        positions: Optional[torch.Tensor] = None, table: Optional[torch.Tensor] = None, rot_dims: int = 0,
+                        unit_eps: Optional[float] = None) -> torch.Tensor:
+        """q or k on their way into a recurrence, as float32 ``[T, n_heads * head_dim]``: with ``unit_eps`` every head
+        becomes ``x / sqrt(sum(x^2) + unit_eps)``; with ``table`` (``[positions, rot_dims / 2, 2]`` of cos and sin) the
+        first ``rot_dims`` coordinates of every head turn by the token's position, coordinate ``i`` paired with
+        ``i + rot_dims / 2``.  The result is multiplied by ``scale``."""
+        ldx = self._rows_view(x, "recurrence input")
+        _need(x.shape[1] == n_heads * head_dim, "recurrence_prep: x [T, n_heads * head_dim]")
+        unit = unit_eps is not None
+        rows = 0
+        if not unit and rot_dims:
+            _cuda_contig(table, "rotation table", torch.float32)
+            _cuda_contig(positions, "positions", torch.int32)
+            _need(table.dim() == 3 and table.shape[1] == rot_dims // 2 and table.shape[2] == 2 and positions.numel() == x.shape[0],
+                  "rotation table must be [positions, rot_dims / 2, 2], one position per token")
+            rows = table.shape[0]
+        else:
+            table = positions = None
+            rot_dims = 0
+        out = torch.empty((x.shape[0], n_heads * head_dim), dtype=torch.float32, device=x.device)
+        rc = self._lib("matrix_state").tl_recurrence_prep(
+            _ptr(x), _DT[x.dtype], ldx, _ptr(out), _ptr(positions), _ptr(table), rows, x.shape[0], n_heads, head_dim, rot_dims,
+            1 if unit else 0, ctypes.c_float(unit_eps or 0.0), ctypes.c_float(scale), _stream())
+        _check(rc, "recurrence_prep")
+        self.launches += 1
+        return out
+
+    @_timed
+    def linear_recurrence(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor,
+                          state_slot: torch.Tensor, fresh: torch.Tensor, *, n_seqs: int, max_q_len: int,
+                          decay: Optional[torch.Tensor] = None, beta_logits: Optional[torch.Tensor] = None,
+                          decay_logits: Optional[torch.Tensor] = None, decay_rate: Optional[torch.Tensor] = None,
+                          decay_bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """A matrix ``S`` (``dk x dv``, float32) per head and request that every token updates and then reads,
+        ``o = S^T q``.  With ``decay`` (float32 ``[H]``): ``S <- decay_h S + k v^T``.  Otherwise the gated delta rule:
+        ``S <- g S; u = beta (v - S^T k); S <- S + k u^T`` with ``beta = sigmoid(beta_logits)`` and
+        ``g = exp(-decay_rate softplus(decay_logits + decay_bias))`` (logits ``[T, H]``, the rest float32 ``[H]``).
+        ``q``, ``k``: float32 ``[T, G * dk]``, ``G`` heads each shared by ``H / G`` value heads; ``v``: ``[T, H * dv]``;
+        ``state``: ``[slots, H, dk, dv]``, read (zeros where ``fresh``) and left updated.  Returns float32 ``[T, H * dv]``."""
+        _cuda_contig(q, "q", torch.float32)
+        _cuda_contig(k, "k", torch.float32)
+        ldv = self._rows_view(v, "v")
+        _need(state.dim() == 4, "state must be [slots, heads, dk, dv]")
+        H, dk, dv = state.shape[1:]
+        pitch = self._state_view(state, H * dk * dv, "recurrence state")
+        T = q.shape[0]
+        _need(q.dim() == 2 and q.shape == k.shape and q.shape[1] % dk == 0 and v.shape == (T, H * dv), "linear_recurrence: sizes")
+        G = q.shape[1] // dk
+        _need(G > 0 and H % G == 0, f"{H} value heads cannot share {G} heads of q and k")
+        _need(dk <= 256, f"linear_recurrence keeps a head's state in registers: key size {dk} exceeds 256")
+        self._seq_index(q_start, state_slot, fresh, n_seqs)
+        delta = decay is None
+        ldg = ctypes.c_longlong(0)
+        if delta:
+            for t, name in ((decay_rate, "decay_rate"), (decay_bias, "decay_bias")):
+                _cuda_contig(t, name, torch.float32)
+                _need(t.numel() == H, f"{name}: one number per head")
+            ldg = self._rows_view(beta_logits, "beta_logits")
+            _need(self._rows_view(decay_logits, "decay_logits").value == ldg.value and beta_logits.shape == (T, H)
+                  and decay_logits.shape == (T, H) and beta_logits.dtype == v.dtype and decay_logits.dtype == v.dtype,
+                  "beta_logits and decay_logits must be [T, H] of v's dtype with one row pitch")
+        else:
+            _cuda_contig(decay, "decay", torch.float32)
+            _need(decay.numel() == H, "decay: one number per head")
+        out = torch.empty((T, H * dv), dtype=torch.float32, device=q.device)
+        rc = self._lib("matrix_state").tl_linear_recurrence(
+            _ptr(q), _ptr(k), _ptr(v), _DT[v.dtype], ldv, _ptr(beta_logits), _ptr(decay_logits), ldg,
+            _ptr(decay_rate if delta else decay), _ptr(decay_bias), _ptr(state), pitch, _ptr(q_start), _ptr(state_slot), _ptr(fresh),
+            _ptr(out), T, n_seqs, H, G, dk, dv, 1 if delta else 0, _stream())
+        _check(rc, "linear_recurrence")
+        self.launches += 1
+        return out
+
+    @_timed
+    def head_norm_gate(self, o: torch.Tensor, gate: torch.Tensor, weight: Optional[torch.Tensor], eps: float, *, head_dim: int,
+                       out_dtype: torch.dtype) -> torch.Tensor:
+        """Every head (``head_dim`` numbers) of ``o`` (float32 ``[T, H * head_dim]``) divided by its root mean square,
+        times ``weight`` (float32 ``[head_dim]``, shared by the heads; ``None``: no weight), times ``silu(gate)``."""
+        _cuda_contig(o, "recurrence output", torch.float32)
+        ldg = self._rows_view(gate, "gate")
+        _need(o.dim() == 2 and o.shape[1] % head_dim == 0 and gate.shape == o.shape, "head_norm_gate: o and gate [T, H * head_dim]")
+        _need(out_dtype in _DT and (out_dtype == gate.dtype or gate.dtype == torch.float32), "head_norm_gate cannot widen a bfloat16 gate")
+        if weight is not None:
+            _cuda_contig(weight, "head norm weight", torch.float32)
+            _need(weight.numel() == head_dim, "the head norm's weight has head_dim numbers")
+        out = torch.empty(o.shape, dtype=out_dtype, device=o.device)
+        rc = self._lib("matrix_state").tl_head_norm_gate(_ptr(o), _ptr(gate), _DT[gate.dtype], ldg, _ptr(weight), _ptr(out), _DT[out_dtype],
+                                                        o.shape[0], o.shape[1] // head_dim, head_dim, ctypes.c_float(eps), _stream())
+        _check(rc, "head_norm_gate")
+        self.launches += 1
+        return out
+
+    @_timed
+    def stream_add(self, h: torch.Tensor, *, normed, coef: float, eps: float, plain, out_dtype: torch.dtype) -> torch.Tensor:
+        """``h += coef * sum_i t_i / sqrt(mean(t_i^2) + eps) * w_i + sum_j p_j`` in place (float32), one kernel:
+        ``normed`` is up to two ``(t_i, w_i)`` (``[T, dim]``, float32 ``[dim]``), ``plain`` up to three ``[T, dim]``
+        tensors.  Returns the new stream in ``out_dtype`` (``h`` itself for float32)."""
+        _cuda_contig(h, "residual stream", torch.float32)
+        _need(h.dim() == 2 and len(normed) <= 2 and len(plain) <= 3, "stream_add: at most two normed and three plain terms")
+        _need(out_dtype in _DT, f"stream_add: output dtype {out_dtype} unsupported")
+        for t, w in normed:
+            _cuda_contig(t, "normed term")
+            _cuda_contig(w, "norm weight", torch.float32)
+            _need(t.shape == h.shape and t.dtype in _DT and w.numel() == h.shape[1], "a normed term has the stream's shape")
+        for t in plain:
+            _cuda_contig(t, "plain term")
+            _need(t.shape == h.shape and t.dtype in _DT, "a plain term has the stream's shape")
+        n, m = len(normed), len(plain)
+        np_ = (ctypes.c_void_p * 2)(*[t.data_ptr() for t, _w in normed])
+        nd = (ctypes.c_int * 2)(*[_DT[t.dtype] for t, _w in normed])
+        nw = (ctypes.c_void_p * 2)(*[w.data_ptr() for _t, w in normed])
+        pp = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in plain])
+        pd = (ctypes.c_int * 3)(*[_DT[t.dtype] for t in plain])
+        rows = None if out_dtype == torch.float32 else torch.empty(h.shape, dtype=out_dtype, device=h.device)
+        rc = self._lib("stream_sum").tl_stream_add(_ptr(h), np_, nd, nw, n, pp, pd, m, ctypes.c_float(coef), ctypes.c_float(eps),
+                                                  _ptr(rows), h.shape[0], h.shape[1], _stream())
+        _check(rc, "stream_add")
+        self.launches += 1
+        return h if rows is None else rows
+
+    @_timed
+    def polynorm(self, z: torch.Tensor, coef: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+        """``a N(z) + b N(z^2) + c N(z^3) + e`` over every row, ``N(y) = y / sqrt(mean(y^2) + eps)``, powers element by
+        element; ``coef`` is float32 ``(a, b, c, e)``."""
+        _cuda_contig(z, "polynorm input")
+        _cuda_contig(coef, "polynorm coefficients", torch.float32)
+        _need(z.dim() == 2 and z.dtype in _DT and coef.numel() == 4, "polynorm: z [T, width], four coefficients")
+        _need(out_dtype in _DT and (out_dtype == z.dtype or z.dtype == torch.float32), "polynorm cannot widen bfloat16 input")
+        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
+        rc = self._lib("stream_sum").tl_polynorm(_ptr(z), _DT[z.dtype], _ptr(coef), _ptr(out), _DT[out_dtype], z.shape[0], z.shape[1],
+                                                ctypes.c_float(eps), _stream())
+        _check(rc, "polynorm")
+        self.launches += 1
+        return out
+
+    @_timed
+    def side_gate(self, u: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """``gelu_tanh(u) * table[token]``: ``u`` ``[T, s]``, ``table`` ``[vocab, s]``, both of ``out_dtype``."""
+        _cuda_contig(u, "side gate input", out_dtype)
+        _cuda_contig(table, "side table", out_dtype)
+        _cuda_contig(token_ids, "token ids", torch.int32)
+        _need(out_dtype in _DT and u.dim() == 2 and table.dim() == 2 and table.shape[1] == u.shape[1] and token_ids.numel() == u.shape[0],
+              "side_gate: u [T, s], table [vocab, s], one token per row")
+        out = torch.empty(u.shape, dtype=out_dtype, device=u.device)
+        rc = self._lib("stream_sum").tl_side_gate(_ptr(u), _ptr(token_ids), _ptr(table), _ptr(out), _DT[out_dtype], u.shape[0], u.shape[1],
+                                                 table.shape[0], _stream())
+        _check(rc, "side_gate")
+        self.launches += 1
+        return out
+
     # ----------------------------------------------------------------- experts
     @_timed
     def moe_route(self, x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], *, n_experts: int,
-                  top: int, scale: float, renormalize: bool, shared_gate: bool):
+                  top: int, scale: float, renormalize: bool, shared_gate: bool, logit_bias: Optional[torch.Tensor] = None):
         """Router of a layer of experts: ``s = softmax(w_router[:E] x)`` in float32, the ``top`` experts
         with the largest ``s + correction`` chosen, weights ``s * scale`` (over their sum with
-        ``renormalize``); with ``shared_gate`` the row ``w_router[E]`` gives ``sigmoid(.)`` per token.
+        ``renormalize``); with ``shared_gate`` the row ``w_router[E]`` gives ``sigmoid(.)`` per token.  ``logit_bias``
+        (float32 ``[E]``) is added to the logits first.  (With ``renormalize`` and a scale of one the weights are
+        the softmax over the chosen logits alone.)
         Returns ``(chosen int32 [T, top], weights float32 [T, top], gate float32 [T] or None)``."""
         _cuda_contig(x, "router input")
         _cuda_contig(w_router, "router weight", torch.float32)
@@ -658,6 +867,9 @@ class NativeOps:
         if correction is not None:
             _cuda_contig(correction, "correction", torch.float32)
             _need(correction.numel() == n_experts, "one correction per expert")
+        if logit_bias is not None:
+            _cuda_contig(logit_bias, "logit_bias", torch.float32)
+            _need(logit_bias.numel() == n_experts, "one logit bias per expert")
         T, dim = x.shape
         rows = w_router.shape[0]
         lib = self._lib("moe")
@@ -678,7 +890,7 @@ class NativeOps:
         chosen = torch.empty((T, top), dtype=torch.int32, device=x.device)
         weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
         gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate else None
-        rc = lib.tl_moe_select(_ptr(logits), _ptr(correction), _ptr(chosen), _ptr(weights), _ptr(gate), T, n_experts, top,
+        rc = lib.tl_moe_select(_ptr(logits), _ptr(correction), _ptr(logit_bias), _ptr(chosen), _ptr(weights), _ptr(gate), T, n_experts, top,
                                ctypes.c_float(scale), 1 if renormalize else 0, _stream())
         _check(rc, "moe_select")
         self.launches += 1
@@ -689,9 +901,11 @@ class NativeOps:
     @_timed
     def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
                     w_down: torch.Tensor, *, activation: str, shared: Optional[torch.Tensor] = None,
-                    shared_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+                    shared_gate: Optional[torch.Tensor] = None, gated: bool = False) -> torch.Tensor:
         """``out[t] = sum_k weights[t, k] * down_e(act(up_e x[t]))`` with ``e = chosen[t, k]``, plus
         ``shared[t]`` (``[T, dim]`` or float32 partial sums) times ``shared_gate[t]`` where given.
+        With ``gated`` an expert is ``down_e(act(gate_e x) * up_e x)`` and ``w_up`` is ``[E, 2 * hidden, dim]``, an expert's
+        rows being ``[gate; up]``.
         ``w_up`` is ``[E, hidden, dim]``; ``w_down`` is ``[dim, >= E * hidden]``, expert ``e``'s matrix being
         the columns ``e * hidden .. (e + 1) * hidden`` (the layout in which all experts are one
         matrix too).  The (token, choice) pairs are sorted by expert on the device and both products
@@ -708,8 +922,10 @@ class NativeOps:
         T, dim = x.shape
         top = chosen.shape[1]
         _need(top <= 64, f"a token may use at most 64 experts, got {top}")
-        E, hidden = w_up.shape[0], w_up.shape[1]
-        _need(w_up.shape == (E, hidden, dim) and w_down.dim() == 2 and w_down.shape[0] == dim and w_down.shape[1] >= E * hidden,
+        E, up_rows = w_up.shape[0], w_up.shape[1]
+        _need(not gated or up_rows % 2 == 0, "gated experts: w_up [E, 2 * hidden, dim]")
+        hidden = up_rows // 2 if gated else up_rows
+        _need(w_up.shape == (E, up_rows, dim) and w_down.dim() == 2 and w_down.shape[0] == dim and w_down.shape[1] >= E * hidden,
               "experts: w_up [E, hidden, dim], w_down [dim, >= E * hidden]")
         ldd = w_down.shape[1]
         lib = self._lib("moe")
@@ -725,13 +941,16 @@ class NativeOps:
             xs = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
             _check(lib.tl_moe_gather(_ptr(x), _DT[x.dtype], _ptr(order), _ptr(xs), pairs, dim, top, _stream()), "moe_gather")
             self.launches += 1
-            u = self.activation(grouped(xs, w_up.transpose(1, 2), offs=ends, out_dtype=x.dtype), activation)
+            u = grouped(xs, w_up.transpose(1, 2), offs=ends, out_dtype=x.dtype)
+            u = self.gated_act(u, activation) if gated else self.activation(u, activation)
             y = grouped(u, w_down.as_strided((E, hidden, dim), (hidden, 1, ldd)), offs=ends, out_dtype=x.dtype)
         else:
-            u = torch.empty((pairs, hidden), dtype=x.dtype, device=x.device)
-            _check(lib.tl_moe_gemm(_ptr(x), _ptr(w_up), _ptr(u), _DT[x.dtype], _ptr(tiles), _ptr(order), top, pairs, E, hidden, dim,
-                                   self._ACTS[activation], ctypes.c_longlong(hidden * dim), ctypes.c_longlong(dim), _stream()),
-                   "moe_gemm (up)")
+            u = torch.empty((pairs, up_rows), dtype=x.dtype, device=x.device)
+            _check(lib.tl_moe_gemm(_ptr(x), _ptr(w_up), _ptr(u), _DT[x.dtype], _ptr(tiles), _ptr(order), top, pairs, E, up_rows, dim,
+                                   -1 if gated else self._ACTS[activation], ctypes.c_longlong(up_rows * dim), ctypes.c_longlong(dim),
+                                   _stream()), "moe_gemm (up)")
+            if gated:
+                u = self.gated_act(u, activation)
             y = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
             _check(lib.tl_moe_gemm(_ptr(u), _ptr(w_down), _ptr(y), _DT[x.dtype], _ptr(tiles), _ptr(order), 0, pairs, E, dim, hidden,
                                    -1, ctypes.c_longlong(hidden), ctypes.c_longlong(ldd), _stream()), "moe_gemm (down)")

@@ -120,7 +120,9 @@ class GatedBiasedAttention(Mixer):
     * projections ``wq, wk, wv`` with optional biases (``qkv_bias``), keys and values of different
       sizes (``head_dim``, ``v_head_dim``);
     * optionally an RMS norm over the *whole* projected row of q and of k (``qk_norm``: before the
-      row is cut into heads; plain weights ``q_norm.weight``, ``k_norm.weight``);
+      row is cut into heads; plain weights ``q_norm.weight``, ``k_norm.weight``), or, with
+      ``qk_norm="head"``, over every head of q and of k by itself, the weights (``head_dim`` numbers
+      each) shared by all heads;
     * score ``= q . k * scale`` plus, with ``distance_bias``, a learned bias by distance and head
       (tensor ``distance_bias`` ``[rows, n_heads]``, row chosen by :func:`distance_buckets`; the scale
       does not touch it; ``bias_rows=None`` takes the number of rows from the stored table);
@@ -135,7 +137,7 @@ class GatedBiasedAttention(Mixer):
 
     def __init__(self, env: BuildEnv, *, dim: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  v_head_dim: Optional[int] = None, scale: float, window: Optional[int] = None, keep_first: int = 0,
-                 qkv_bias: bool = False, qk_norm: bool = False, norm_eps: float = 1e-6,
+                 qkv_bias: bool = False, qk_norm=False, norm_eps: float = 1e-6,
                  distance_bias: bool = False, bias_rows: Optional[int] = None, bias_far: float = 0.0,
                  gated: bool = False):
         if n_heads % n_kv_heads != 0:
@@ -150,6 +152,7 @@ class GatedBiasedAttention(Mixer):
         self.window = None if window is None else int(window)
         self.keep_first = int(keep_first)
         self.qkv_bias, self.qk_norm, self.gated = bool(qkv_bias), bool(qk_norm), bool(gated)
+        self.norm_per_head = qk_norm == "head"
         self.norm_eps = float(norm_eps)
         self.has_bias = bool(distance_bias)
         self.bias_rows, self.bias_far = (None if bias_rows is None else int(bias_rows)), float(bias_far)
@@ -182,7 +185,10 @@ class GatedBiasedAttention(Mixer):
             out.update({"wq.bias": ExpectedTensor((self.n_q,)), "wk.bias": ExpectedTensor((self.n_k,)),
                         "wv.bias": ExpectedTensor((self.n_v,))})
         if self.qk_norm:
-            out.update({"q_norm.weight": ExpectedTensor((self.n_q,)), "k_norm.weight": ExpectedTensor((self.n_k,))})
+            if self.norm_per_head:
+                out.update({"q_norm.weight": ExpectedTensor((self.head_dim,)), "k_norm.weight": ExpectedTensor((self.head_dim,))})
+            else:
+                out.update({"q_norm.weight": ExpectedTensor((self.n_q,)), "k_norm.weight": ExpectedTensor((self.n_k,))})
         if self.has_bias:
             out["distance_bias"] = ExpectedTensor((-1 if self.bias_rows is None else self.bias_rows, self.n_heads))
         if self.gated:
@@ -211,7 +217,7 @@ class GatedBiasedAttention(Mixer):
         q, gate = ops.project_and_store(
             proj, n_q=self.n_q, n_k=self.n_k, n_v=self.n_v, n_extra=self.n_g, bias=self.b_in,
             q_norm=self.q_norm_w, k_norm=self.k_norm_w, eps=self.norm_eps,
-            k_pages=cache.k_pages if cache.writes else None, v_pages=cache.v_pages if cache.writes else None,
+            norm_head_dim=self.head_dim if self.norm_per_head else None, k_pages=cache.k_pages if cache.writes else None, v_pages=cache.v_pages if cache.writes else None,
             slot_mapping=cache.slot_mapping, page_size=cache.page_size, out_dtype=self.env.dtype)
         o = ops.paged_attention(
             q.view(-1, self.n_heads, self.head_dim), cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start,

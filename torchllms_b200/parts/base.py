@@ -105,10 +105,49 @@ class CacheNeed:
 
 @dataclass(frozen=True)
 class StateNeed:
-    """Per-request state of fixed size (``shape`` elements of ``dtype``), kept in a slot."""
+    """Per-request state of fixed size (``shape`` elements of ``dtype``), kept in a slot.
+
+    A need may be several states laid end to end in one flat row (:func:`join_states`): ``fields``
+    then lists ``(name, offset, shape)`` of each, and :func:`state_field` cuts one out of the rows
+    the cache manager hands over.  A field may itself be a joined need (a block's own state beside
+    its mixer's): whoever owns it cuts further with its own need."""
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+    fields: Tuple[Tuple[str, int, Tuple[int, ...]], ...] = ()
+
+    @property
+    def numel(self) -> int:
+        n = 1
+        for s in self.shape:
+            n *= int(s)
+        return n
+
+
+def join_states(named) -> Optional[StateNeed]:
+    """One flat float32 need for ``[(name, need or None), ...]``; ``None`` if nobody wants state."""
+    fields, off = [], 0
+    for name, need in named:
+        if need is None:
+            continue
+        if need.dtype != torch.float32:
+            raise ValueError(f"state '{name}': joined states are float32, got {need.dtype}")
+        fields.append((name, off, tuple(int(s) for s in need.shape)))
+        off += need.numel
+    if not fields:
+        return None
+    return StateNeed((off,), torch.float32, tuple(fields))
+
+
+def state_field(state: torch.Tensor, need: StateNeed, name: str) -> torch.Tensor:
+    """The rows of one field: ``[slots, *shape]``, a view whose rows lie a whole joined row apart."""
+    for field_name, off, shape in need.fields:
+        if field_name == name:
+            n = 1
+            for s in shape:
+                n *= s
+            return state[:, off:off + n].unflatten(1, shape)
+    raise KeyError(f"no state field {name!r}; there are: {', '.join(f[0] for f in need.fields) or '(none)'}")
 
 
 class Part:

@@ -9,12 +9,15 @@ on the residual so the following norm adds them in 32-bit in the same pass.
 
 from __future__ import annotations
 
+import dataclasses
 from typing import Dict, Mapping, Optional
 
 import torch
 
+from ..kernels.lazy import NormedSum, PendingProduct
 from ..weights.loader import ExpectedTensor
-from .base import FEED_FORWARDS, MIXERS, NORMS, Block, BuildEnv, Residual, register_block
+from .base import (FEED_FORWARDS, MIXERS, NORMS, Block, BuildEnv, Residual, StateNeed, as_compute, join_states,
+                   register_block, state_field)
 from .norm import RMSNorm
 from .spec import PartSpec
 
@@ -214,3 +217,118 @@ class SandwichBlock(Block):
             else:
                 self.env.ops.depth_mix(history, self.depth_coef, self.depth_inputs, nxt)
             residual.h, residual.rows, residual.level = nxt, None, level + 1
+
+
+@register_block("parallel")
+class ParallelBlock(Block):
+    """One norm in front, both sublayers reading its output, one sum: with ``h = norm(x)``,
+    ``x += mixer(h') + ff(h)``.  A layer may have no feed-forward.
+
+    ``input_conv_taps = n``: what the mixer reads is ``h' = h + conv(h)``, a causal convolution over
+    time on every channel (tensor ``input_conv_tensor`` ``[dim, n]``, the last column the current
+    token's, zeros before a request's start); the last ``n - 1`` rows of ``h`` are part of the
+    request's state.  The feed-forward reads ``h`` as it is.
+
+    ``token_side_dim = s``: after the sum the layer takes an input of its own from the token:
+    ``g = gelu_tanh(W_gate x) * table[token]`` (``s`` numbers), ``y = W_proj g``, ``x += norm(y)`` with
+    a plain-weight RMS norm.  Tensors ``<side_prefix>.table [vocab, s]``, ``.gate.weight``,
+    ``.proj.weight``, ``.norm.weight``.
+
+    The sum is one kernel in 32-bit that also leaves the new stream in the activation dtype; a mixer
+    that returns normed terms (:class:`~torchllms_b200.kernels.lazy.NormedSum`) has its norms taken
+    there.  The side input's norm kernel also takes the next layer's input norm."""
+
+    def __init__(self, env: BuildEnv, *, mixer: PartSpec, feed_forward: Optional[PartSpec], norm: PartSpec,
+                 mixer_prefix: str, ffn_prefix: str, norm_prefix: str, input_conv_taps: int = 0,
+                 input_conv_tensor: str = "input_conv", token_side_dim: int = 0, token_side_vocab: int = 0,
+                 token_side_eps: float = 1e-6, side_prefix: str = "side"):
+        self.env = env
+        self.mixer = MIXERS.build(mixer, env)
+        self.norm = NORMS.build(norm, env)
+        self.input_norm = self.norm
+        self.feed_forward = None if feed_forward is None else FEED_FORWARDS.build(feed_forward, env)
+        self._subparts = [(mixer_prefix, self.mixer), (norm_prefix, self.norm)]
+        if self.feed_forward is not None:
+            self._subparts.append((ffn_prefix, self.feed_forward))
+        self.taps, self.conv_tensor = int(input_conv_taps), input_conv_tensor
+        self.side_dim, self.side_vocab, self.side_prefix = int(token_side_dim), int(token_side_vocab), side_prefix
+        self.side_norm = None
+        if self.side_dim:
+            self.side_norm = NORMS.build(PartSpec("rmsnorm", {"dim": env.dim, "eps": float(token_side_eps)}), env)
+            self._subparts.append((f"{side_prefix}.norm", self.side_norm))
+        self._need = join_states([("input_conv", StateNeed((self.taps - 1, env.dim)) if self.taps > 1 else None),
+                                  ("mixer", self.mixer.state_need())])
+        self.graph_safe = all(sub.graph_safe for _p, sub in self._subparts)
+        self.conv_w = self.side_table = self.side_gate_w = self.side_proj_w = None
+
+    def cache_need(self):
+        return self.mixer.cache_need()
+
+    def state_need(self):
+        return self._need
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out: Dict[str, ExpectedTensor] = {}
+        for prefix, sub in self._subparts:
+            for name, e in sub.expected_tensors().items():
+                out[f"{prefix}.{name}"] = e
+        if self.taps:
+            out[self.conv_tensor] = ExpectedTensor((self.env.dim, self.taps))
+        if self.side_dim:
+            p = self.side_prefix
+            out[f"{p}.table"] = ExpectedTensor((self.side_vocab, self.side_dim))
+            out[f"{p}.gate.weight"] = ExpectedTensor((self.side_dim, self.env.dim))
+            out[f"{p}.proj.weight"] = ExpectedTensor((self.env.dim, self.side_dim))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        for prefix, sub in self._subparts:
+            sub.load({name: tensors[f"{prefix}.{name}"] for name in sub.expected_tensors()})
+        if self.taps:
+            self.conv_w = tensors[self.conv_tensor].to(device=self.env.device, dtype=torch.float32).contiguous()
+        if self.side_dim:
+            p = self.side_prefix
+            self.side_table = as_compute(tensors[f"{p}.table"], self.env)
+            self.side_gate_w = as_compute(tensors[f"{p}.gate.weight"], self.env)
+            self.side_proj_w = as_compute(tensors[f"{p}.proj.weight"], self.env)
+
+    def weight_bytes(self) -> int:
+        extra = sum(t.numel() * t.element_size() for t in (self.side_gate_w, self.side_proj_w) if t is not None)
+        return sum(sub.weight_bytes() for _p, sub in self._subparts) + extra
+
+    def forward(self, residual: Residual, ctx, cache) -> None:
+        ops = self.env.ops
+        if residual.delta is not None:
+            raise RuntimeError("a parallel block cannot follow a block that leaves its sum pending")
+        if residual.normed is not None and residual.normed[0] is self.norm:
+            h = residual.normed[1]                       # the block before took this norm along with its last kernel
+        else:
+            h = self.norm.forward(residual)
+        residual.normed = None
+        hm = h
+        if self.taps:
+            state = state_field(cache.state, self._need, "input_conv") if self.taps > 1 else None
+            hm = ops.short_conv(h, self.conv_w, state, ctx.q_start, ctx.state_slot, ctx.fresh, n_seqs=ctx.n_seqs,
+                                max_q_len=ctx.max_q_len, activation=None, residual=True, out_dtype=self.env.dtype)
+        mixer_state = None if self.mixer.state_need() is None else state_field(cache.state, self._need, "mixer")
+        y = self.mixer.forward(hm, ctx, dataclasses.replace(cache, state=mixer_state))
+        f = None if self.feed_forward is None else self.feed_forward.forward(h, ctx)
+        normed, coef, eps, plain = (), 1.0, 0.0, []
+        for term in (y, f):
+            if isinstance(term, NormedSum):
+                normed, coef, eps = term.terms, term.coef, term.eps
+            elif isinstance(term, PendingProduct):
+                plain.append(term.take(ops, partials_ok=False))
+            elif term is not None:
+                plain.append(term)
+        rows = ops.stream_add(residual.h, normed=normed, coef=coef, eps=eps, plain=tuple(plain), out_dtype=self.env.dtype)
+        residual.rows = rows
+        if not self.side_dim:
+            return
+        u = ops.linear(rows, self.side_gate_w)
+        g = ops.side_gate(u, ctx.token_ids, self.side_table, out_dtype=self.env.dtype)
+        follow = residual.next_norm
+        if isinstance(follow, RMSNorm):
+            residual.normed = (follow, self.side_norm.fold_normed(residual, PendingProduct(g, self.side_proj_w), then=follow))
+        else:
+            self.side_norm.fold_normed(residual, PendingProduct(g, self.side_proj_w), want_rows=False)

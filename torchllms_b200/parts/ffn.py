@@ -116,3 +116,35 @@ class GatedLinearUnit(FeedForward):
     def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
         y = self.env.ops.linear_gated_act(x, self.w_gate_up, activation=self.activation)
         return PendingProduct(y, self.w_down)       # the down projection is left to the norm that follows
+
+
+@register_feed_forward("polynorm")
+class PolyNormFeedForward(FeedForward):
+    """Dense feed-forward without a gate whose activation is a polynomial of normalised powers:
+    ``down(a N(z) + b N(z^2) + c N(z^3) + e)`` with ``z = up x``, powers taken element by element and
+    ``N(y) = y / sqrt(mean(y^2) + eps)`` over a token's ``hidden`` values.  The four numbers are the
+    stored tensor ``act``; the three norms are float32 and one kernel."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, hidden: int, eps: float):
+        self.env = env
+        self.dim, self.hidden, self.eps = int(dim), int(hidden), float(eps)
+        self.w_up = self.w_down = self.coef = None
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        return {"up.weight": ExpectedTensor((self.hidden, self.dim)), "down.weight": ExpectedTensor((self.dim, self.hidden)),
+                "act": ExpectedTensor((4,))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up = as_compute(tensors["up.weight"], self.env)
+        self.w_down = as_compute(tensors["down.weight"], self.env)
+        self.coef = tensors["act"].to(device=self.env.device, dtype=torch.float32).contiguous()
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_up, self.w_down))
+
+    def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
+        ops = self.env.ops
+        y = ops.polynorm(ops.linear(x, self.w_up), self.coef, self.eps, out_dtype=self.env.dtype)
+        return PendingProduct(y, self.w_down)

@@ -24,9 +24,10 @@ EXPERT_ACTIVATIONS = ("relu2", "silu", "gelu_tanh")
 
 @register_feed_forward("routed_experts")
 class RoutedExperts(FeedForward):
-    """``n_experts`` feed-forwards ``down_e(act(up_e x))`` without biases; a token uses ``top`` of them.
+    """``n_experts`` feed-forwards ``down_e(act(up_e x))`` without biases (with ``gated``:
+    ``down_e(act(gate_e x) * up_e x)``); a token uses ``top`` of them.
 
-    * router logits ``z = W_router x`` and scores ``s = softmax(z)`` over all experts, in float32;
+    * router logits ``z = W_router x`` (plus the stored vector ``router.bias`` with ``router_bias``) and scores ``s = softmax(z)`` over all experts, in float32;
     * the experts with the largest ``s + correction`` are chosen (``choice_correction``: a stored
       vector ``correction`` that steers the choice and nothing else);
     * their weights are ``s * router_scale``, divided by their sum first with ``renormalize``;
@@ -41,7 +42,8 @@ class RoutedExperts(FeedForward):
 
     def __init__(self, env: BuildEnv, *, dim: int, n_experts: int, top: int, hidden: int, activation: str = "relu2",
                  router_scale: float = 1.0, choice_correction: bool = False, renormalize: bool = False,
-                 shared_hidden: Optional[int] = None, shared_gate: bool = False):
+                 shared_hidden: Optional[int] = None, shared_gate: bool = False, gated: bool = False,
+                 router_bias: bool = False):
         if activation not in EXPERT_ACTIVATIONS:
             raise ValueError(f"unknown expert activation {activation!r}; known: {', '.join(EXPERT_ACTIVATIONS)}")
         if not 0 < top <= n_experts:
@@ -55,6 +57,11 @@ class RoutedExperts(FeedForward):
         self.choice_correction, self.renormalize = bool(choice_correction), bool(renormalize)
         self.shared_hidden = None if not shared_hidden else int(shared_hidden)
         self.shared_gate = bool(shared_gate)
+        self.gated, self.router_bias = bool(gated), bool(router_bias)
+        if self.gated and self.shared_hidden:
+            raise ValueError("gated experts beside a shared expert are not built")
+        self.up_rows = self.hidden * (2 if self.gated else 1)      # rows of one expert's stacked [gate; up]
+        self.logit_bias: Optional[torch.Tensor] = None
         self.w_router: Optional[torch.Tensor] = None       # float32 [E (+ 1), dim]: the gate's row rides along
         self.correction: Optional[torch.Tensor] = None
         # every expert's up matrix stacked, the shared expert's last: [E * hidden + shared, dim]; the down matrices
@@ -70,7 +77,11 @@ class RoutedExperts(FeedForward):
         out = {"router.weight": ExpectedTensor((self.n_experts, self.dim))}
         if self.choice_correction:
             out["correction"] = ExpectedTensor((self.n_experts,))
+        if self.router_bias:
+            out["router.bias"] = ExpectedTensor((self.n_experts,))
         for e in range(self.n_experts):
+            if self.gated:
+                out[f"experts.{e}.gate.weight"] = ExpectedTensor((self.hidden, self.dim))
             out[f"experts.{e}.up.weight"] = ExpectedTensor((self.hidden, self.dim))
             out[f"experts.{e}.down.weight"] = ExpectedTensor((self.dim, self.hidden))
         if self.shared_hidden:
@@ -88,7 +99,11 @@ class RoutedExperts(FeedForward):
         self.w_router = torch.cat(rows).contiguous()
         if self.choice_correction:
             self.correction = tensors["correction"].to(**f32).contiguous()
+        if self.router_bias:
+            self.logit_bias = tensors["router.bias"].to(**f32).contiguous()
         ups = [as_compute(tensors[f"experts.{e}.up.weight"], self.env) for e in range(self.n_experts)]
+        if self.gated:        # an expert's rows are [gate; up], so that one product yields both
+            ups = [torch.cat([as_compute(tensors[f"experts.{e}.gate.weight"], self.env), up]) for e, up in enumerate(ups)]
         downs = [as_compute(tensors[f"experts.{e}.down.weight"], self.env) for e in range(self.n_experts)]
         if self.shared_hidden:
             ups.append(as_compute(tensors["shared.up.weight"], self.env))
@@ -96,8 +111,8 @@ class RoutedExperts(FeedForward):
             self.w_shared_down = downs[-1]
         self.w_up_all = torch.cat(ups).contiguous()
         self.w_down_all = torch.cat(downs, dim=1).contiguous()
-        n = self.n_experts * self.hidden
-        self.w_up = self.w_up_all[:n].view(self.n_experts, self.hidden, self.dim)
+        n = self.n_experts * self.up_rows
+        self.w_up = self.w_up_all[:n].view(self.n_experts, self.up_rows, self.dim)
         if self.shared_hidden:
             self.w_shared_up = self.w_up_all[n:]
 
@@ -110,8 +125,8 @@ class RoutedExperts(FeedForward):
         ops = self.env.ops
         chosen, weights, gate = ops.moe_route(x, self.w_router, self.correction, n_experts=self.n_experts, top=self.top,
                                               scale=self.router_scale, renormalize=self.renormalize,
-                                              shared_gate=self.shared_gate)
-        if ops.moe_prefers_dense(x.shape[0], self.top, self.n_experts, x.dtype):
+                                              shared_gate=self.shared_gate, logit_bias=self.logit_bias)
+        if not self.gated and ops.moe_prefers_dense(x.shape[0], self.top, self.n_experts, x.dtype):
             # few tokens that touch most experts between them: every expert (and the shared one) as one
             # matrix each way, the rows of experts a token did not choose multiplied by zero
             u = ops.moe_dense_hidden(x, chosen, weights, gate, self.w_up_all, n_experts=self.n_experts, hidden=self.hidden,
@@ -122,4 +137,4 @@ class RoutedExperts(FeedForward):
             u = ops.activation(ops.linear(x, self.w_shared_up, partials_ok=True), self.activation, out_dtype=self.env.dtype)
             shared = ops.linear(u, self.w_shared_down, partials_ok=True)
         return ops.moe_experts(x, chosen, weights, self.w_up, self.w_down_all, activation=self.activation,
-                               shared=shared, shared_gate=gate)
+                               shared=shared, shared_gate=gate, gated=self.gated)

@@ -75,6 +75,9 @@ class ModelSpec:
     embedding_scale: float = 1.0     # the rows of the table enter the stream multiplied by this
     position_tensor: Optional[str] = None   # name of a learned [max_positions, dim] table added to the embedding
     keeps_history: bool = False      # the result of every layer run stays readable by later runs (Residual.history)
+    embedding_norm: Optional[PartSpec] = None        # a norm applied to the table's row: its result is the stream
+    embedding_norm_prefix: str = "embedding_norm"    # prefix of that norm's tensors
+    logit_scale: float = 1.0         # the head's products leave multiplied by this
 
     def __post_init__(self):
         n = len(self.layers)
