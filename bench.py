@@ -312,7 +312,33 @@ def _rakuvik_config(z, vocab, max_len):
     return RakuvikConfig("Rakuvik", vocab, z["dim"], 1e-6, tuple(layers), max_seq_len=max_len)
 
 
-DESIGNS = {"nagolix": ("Nagolix", DESIGN_SIZES, _nagolix_config), "rakuvik": ("Rakuvik", RAKUVIK_SIZES, _rakuvik_config)}
+# Nunosun at the same widths: a parallel layer (sliding-window attention with a table of distances beside a
+# retention) with a PolyNorm feed-forward, then a gated-delta-rule layer with gated experts; the per-token side
+# input and the convolution in front of every mixer as the design has them
+NUNOSUN_SIZES = {
+    "w2048": dict(RAKUVIK_SIZES["w2048"], window=1024, state_heads=16, conv=4, taps=4, side=256),
+    "w4096": dict(RAKUVIK_SIZES["w4096"], window=1024, state_heads=32, conv=4, taps=4, side=256),
+}
+
+
+def _nunosun_config(z, vocab, max_len):
+    from torchllms_b200.models.nunosun import (DeltaConfig, LayerConfig, MlpConfig, NunosunConfig, ParallelConfig,
+                                               RetentionConfig, WindowAttentionConfig)
+    hd, sh = z["head_dim"], z["state_heads"]
+    left = WindowAttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, window=z["window"],
+                                 bias_max=float(z["window"]))
+    right = RetentionConfig(heads=sh, dim=hd, vdim=hd, decay=tuple(1.0 - 2.0 ** -(5 + i % 8) for i in range(sh)), rot_dims=z["rot_dims"],
+                            rot_base=1000000.0)
+    delta = DeltaConfig(heads=sh, kv_heads=z["kv_heads"], dim=hd, vdim=hd, conv=z["conv"])
+    kinds = [(ParallelConfig(left, right), MlpConfig("dense", z["ff"])),
+             (delta, MlpConfig("moe", z["expert_ff"], experts=z["experts"], top=z["top"]))]
+    return NunosunConfig("Nunosun", vocab, z["dim"], 1e-6, z["taps"], z["side"], 1.0,
+                         tuple(LayerConfig(*kinds[i % 2]) for i in range(z["layers"])), max_seq_len=max_len)
+
+
+# design -> (its name, the table of sizes, how its configuration is made, the model it stands beside)
+DESIGNS = {"nagolix": ("Nagolix", DESIGN_SIZES, _nagolix_config, "llama"), "rakuvik": ("Rakuvik", RAKUVIK_SIZES, _rakuvik_config, "llama"),
+           "nunosun": ("Nunosun", NUNOSUN_SIZES, _nunosun_config, "rakuvik")}
 
 
 def design_workload(args, peaks, design="nagolix"):
@@ -322,13 +348,14 @@ def design_workload(args, peaks, design="nagolix"):
     model's time goes (per kernel-library call, from ``ops.profile()``).  Nagolix layers alternate latent
     attention, attention, latent attention reading the first one's latents, attention; Rakuvik layers
     alternate minGRU with a dense feed-forward, differential attention with experts, minGRU with experts,
-    differential attention reading the first one's keys and values with experts."""
+    differential attention reading the first one's keys and values with experts.  Nunosun stands beside
+    Rakuvik, the closest model (recurrent layers, attention, experts), at the same sizes."""
     import torch
     from torchllms_b200.engine.step import StepEntry
     from torchllms_b200.inference import LLM
     from torchllms_b200.models.llama_config import LlamaConfig, RopeScaling
 
-    title, sizes, make_config = DESIGNS[design]
+    title, sizes, make_config, beside = DESIGNS[design]
     vocab, prompt_len, batch = 32000, PROMPT_LEN, args.batch
     steps, warmup = min(args.steps, 64), max(args.warmup, 3)
     max_len = prompt_len + warmup + steps + 64
@@ -337,6 +364,9 @@ def design_workload(args, peaks, design="nagolix"):
     for name, z in sizes.items():
         hd = z["head_dim"]
         configs = {
+            design: make_config(z, vocab, max_len),
+            "rakuvik": _rakuvik_config(z, vocab, max_len),
+        } if beside == "rakuvik" else {
             design: make_config(z, vocab, max_len),
             "llama": LlamaConfig(architecture="LlamaForCausalLM", n_layers=z["layers"], dim=z["dim"], n_heads=z["heads"],
                                  n_kv_heads=z["kv_heads"], head_dim=hd, ffn_hidden=z["ff"], vocab_size=vocab, norm_eps=1e-5,
@@ -401,7 +431,7 @@ def design_workload(args, peaks, design="nagolix"):
             }
             del llm, engine
             torch.cuda.empty_cache()
-    return {"metric": f"{title} beside Llama at equal sizes: prefill and decode tokens/s", "unit": "tokens/s", "n_gpus": 1,
+    return {"metric": f"{title} beside {beside.capitalize()} at equal sizes: prefill and decode tokens/s", "unit": "tokens/s", "n_gpus": 1,
             "dtype": "bf16", "data": "synthetic (uniform random token ids, random weights)",
             "config": {"prompt_len": prompt_len, "batch": batch, "decode_steps": steps, "warmup": warmup, "vocab": vocab,
                        "sizes": sizes}, "sizes": out, "peaks": peaks["source"]}
@@ -416,9 +446,10 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix", "design_rakuvik"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix", "design_rakuvik", "design_nunosun"] + sorted(SERVE),
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate; "
-                         "design_nagolix, design_rakuvik: that design beside the Llama decoder at equal sizes")
+                         "design_nagolix, design_rakuvik: that design beside the Llama decoder at equal sizes; "
+                         "design_nunosun: Nunosun beside Rakuvik at equal sizes")
     ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
     ap.add_argument("--long-contexts", type=lambda t: [int(x) for x in t.split(",") if x], default=[8192, 32768],

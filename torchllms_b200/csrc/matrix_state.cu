@@ -218,12 +218,16 @@ struct RecurrenceParams {
 };
 
 // A CTA per (32 columns, head, request), 4 warps of 8 columns each; a warp's lanes are 8 columns x 4 slices of the
-// key size: lane (jj, s) keeps S[s + 4 r][j] for r < R in registers.  Sums over the key size end with two shuffles.
+// key size: lane (jj, s) keeps S[s R + r][j] for r < R in registers (4 R >= dk; rows past dk stay zero).  q and k of a
+// few tokens lie in shared memory in rows of 4 R floats, zeros past dk, so a lane reads its slice four floats at a
+// time and nothing in the loop over tokens asks where dk ends.  Sums over the key size run as four chains and end
+// with two shuffles.
 template <int R, bool DELTA, typename TV>
 __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceParams p) {
     extern __shared__ __align__(16) float smem[];
     grid_launch_dependents();
     grid_dependency_wait();
+    constexpr int PITCH = 4 * R;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int jj = lane & 7, s = lane >> 3;
     const int h = blockIdx.y, b = blockIdx.z;
@@ -232,9 +236,9 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
     const int g = h / (p.H / p.G);
     const int start = p.q_start[b], len = p.q_start[b + 1] - start;
     if (len <= 0) return;
-    float* sq = smem;                                   // [RC_TOKENS][dk]
-    float* sk = sq + RC_TOKENS * p.dk;                  // [RC_TOKENS][dk]
-    float* sv = sk + RC_TOKENS * p.dk;                  // [RC_TOKENS][RC_COLS]
+    float* sq = smem;                                   // [RC_TOKENS][PITCH]
+    float* sk = sq + RC_TOKENS * PITCH;                 // [RC_TOKENS][PITCH]
+    float* sv = sk + RC_TOKENS * PITCH;                 // [RC_TOKENS][RC_COLS]
     float* sg = sv + RC_TOKENS * RC_COLS;               // [RC_TOKENS]: the token's decay
     float* sb = sg + RC_TOKENS;                         // [RC_TOKENS]: the token's beta
     float* st = p.state + (size_t)p.state_slot[b] * p.state_pitch + (size_t)h * p.dk * p.dv;
@@ -242,7 +246,7 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
     const bool fresh = p.fresh[b] != 0;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = s + 4 * r;
+        const int i = s * R + r;
         S[r] = (!fresh && live && i < p.dk) ? st[(size_t)i * p.dv + j] : 0.f;
     }
     const float fixed = DELTA ? 0.f : p.decay[h];
@@ -251,11 +255,11 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
     for (int t0 = 0; t0 < len; t0 += RC_TOKENS) {
         const int n = min(len - t0, RC_TOKENS);
         __syncthreads();                                // the tokens before have been used
-        for (int e = threadIdx.x; e < n * p.dk; e += NT) {
-            const int tt = e / p.dk, d = e - tt * p.dk;
+        for (int e = threadIdx.x; e < n * PITCH; e += NT) {
+            const int tt = e / PITCH, d = e - tt * PITCH;
             const size_t at = (size_t)(start + t0 + tt) * qk_row + (size_t)g * p.dk + d;
-            sq[e] = p.q[at];
-            sk[e] = p.k[at];
+            sq[e] = d < p.dk ? p.q[at] : 0.f;
+            sk[e] = d < p.dk ? p.k[at] : 0.f;
         }
         for (int e = threadIdx.x; e < n * RC_COLS; e += NT) {
             const int tt = e / RC_COLS, c = e - tt * RC_COLS, col = blockIdx.x * RC_COLS + c;
@@ -270,39 +274,53 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
         }
         __syncthreads();
         for (int tt = 0; tt < n; ++tt) {
-            const float* kt = sk + tt * p.dk;
-            const float* qt = sq + tt * p.dk;
+            const float4* kt = reinterpret_cast<const float4*>(sk + tt * PITCH + s * R);
+            const float4* qt = reinterpret_cast<const float4*>(sq + tt * PITCH + s * R);
             const float vt = sv[tt * RC_COLS + jl];
+            float4 kv[R / 4];
+#pragma unroll
+            for (int r = 0; r < R / 4; ++r) kv[r] = kt[r];
             if (DELTA) {
                 const float gt = sg[tt];
-                float dot = 0.f;
+                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = s + 4 * r;
-                    S[r] *= gt;
-                    if (i < p.dk) dot = fmaf(S[r], kt[i], dot);
+                for (int r = 0; r < R / 4; ++r) {
+                    S[4 * r] *= gt; S[4 * r + 1] *= gt; S[4 * r + 2] *= gt; S[4 * r + 3] *= gt;
+                    d0 = fmaf(S[4 * r], kv[r].x, d0);
+                    d1 = fmaf(S[4 * r + 1], kv[r].y, d1);
+                    d2 = fmaf(S[4 * r + 2], kv[r].z, d2);
+                    d3 = fmaf(S[4 * r + 3], kv[r].w, d3);
                 }
+                float dot = (d0 + d1) + (d2 + d3);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 8);
                 dot += __shfl_xor_sync(0xffffffffu, dot, 16);
                 const float u = sb[tt] * (vt - dot);
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = s + 4 * r;
-                    if (i < p.dk) S[r] = fmaf(kt[i], u, S[r]);
+                for (int r = 0; r < R / 4; ++r) {
+                    S[4 * r] = fmaf(kv[r].x, u, S[4 * r]);
+                    S[4 * r + 1] = fmaf(kv[r].y, u, S[4 * r + 1]);
+                    S[4 * r + 2] = fmaf(kv[r].z, u, S[4 * r + 2]);
+                    S[4 * r + 3] = fmaf(kv[r].w, u, S[4 * r + 3]);
                 }
             } else {
 #pragma unroll
-                for (int r = 0; r < R; ++r) {
-                    const int i = s + 4 * r;
-                    if (i < p.dk) S[r] = fmaf(fixed, S[r], kt[i] * vt);
+                for (int r = 0; r < R / 4; ++r) {
+                    S[4 * r] = fmaf(fixed, S[4 * r], kv[r].x * vt);
+                    S[4 * r + 1] = fmaf(fixed, S[4 * r + 1], kv[r].y * vt);
+                    S[4 * r + 2] = fmaf(fixed, S[4 * r + 2], kv[r].z * vt);
+                    S[4 * r + 3] = fmaf(fixed, S[4 * r + 3], kv[r].w * vt);
                 }
             }
-            float o = 0.f;
+            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-                const int i = s + 4 * r;
-                if (i < p.dk) o = fmaf(S[r], qt[i], o);
+            for (int r = 0; r < R / 4; ++r) {
+                const float4 qv = qt[r];
+                o0 = fmaf(S[4 * r], qv.x, o0);
+                o1 = fmaf(S[4 * r + 1], qv.y, o1);
+                o2 = fmaf(S[4 * r + 2], qv.z, o2);
+                o3 = fmaf(S[4 * r + 3], qv.w, o3);
             }
+            float o = (o0 + o1) + (o2 + o3);
             o += __shfl_xor_sync(0xffffffffu, o, 8);
             o += __shfl_xor_sync(0xffffffffu, o, 16);
             if (s == 0 && live) p.out[(size_t)(start + t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = o;
@@ -310,7 +328,7 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
-        const int i = s + 4 * r;
+        const int i = s * R + r;
         if (live && i < p.dk) st[(size_t)i * p.dv + j] = S[r];
     }
 }
@@ -387,10 +405,11 @@ extern "C" int tl_linear_recurrence(const float* q, const float* k, const void* 
     p.q = q; p.k = k; p.v = v; p.ldv = ldv; p.beta = beta; p.gate = gate; p.ldg = ldg; p.decay = decay; p.decay_bias = decay_bias;
     p.state = state; p.state_pitch = state_pitch; p.q_start = q_start; p.state_slot = state_slot; p.fresh = fresh; p.out = out;
     p.H = heads; p.G = qk_heads; p.dk = dk; p.dv = dv;
-    const size_t smem = ((size_t)2 * RC_TOKENS * dk + RC_TOKENS * RC_COLS + 2 * RC_TOKENS) * sizeof(float);
+    const int need = (dk + 3) / 4;
+    const int rows = need <= 8 ? 8 : need <= 16 ? 16 : need <= 24 ? 24 : need <= 32 ? 32 : need <= 48 ? 48 : 64;   // R of the kernel chosen below
+    const size_t smem = ((size_t)2 * RC_TOKENS * 4 * rows + RC_TOKENS * RC_COLS + 2 * RC_TOKENS) * sizeof(float);
     const dim3 grid((dv + RC_COLS - 1) / RC_COLS, heads, n_seqs), block(NT);
     cudaStream_t s = (cudaStream_t)stream;
-    const int need = (dk + 3) / 4;
 #define TL_REC(R, TV)                                                                                               \
     (delta ? tl_launch(linear_recurrence_kernel<R, true, TV>, grid, block, smem, s, p)                              \
            : tl_launch(linear_recurrence_kernel<R, false, TV>, grid, block, smem, s, p))
