@@ -428,7 +428,7 @@ def random_tensors(cfg: NunosunConfig, seed: int, *, device="cpu", dtype: torch.
         elif init == "side_gain":
             t = 0.3 + t * 0.05
         elif init == "poly":
-            t = torch.tensor([1.0, 0.5, 0.25, 0.0]) + t * 0.1
+            t = torch.tensor([1.0, 0.5, 0.25, 0.0], device=device) + t * 0.1
         yield name, t.to(dtype)
 
 
