@@ -92,6 +92,19 @@ def test_long_decoding_and_a_slot_used_again(tmp_path, backend):
     rp.engine.cache.check_invariants()
 
 
+def test_layers_of_experts_as_one_matrix(tmp_path):
+    """The form a decode batch takes on the GPU (every expert's [gate; up] as one matrix, zeros where a
+    token did not choose an expert), forced for every step over the kernels' twins: the same logits."""
+    from torch_ops import TorchOps
+    from torchllms_b200.engine.replay import Replayer
+    cfg, tensors, folder, page = nc.case_folder(tmp_path, "mixed")
+    tokens = nc.tokens_for(cfg, 40, seed=2)
+    ops = TorchOps()
+    ops.dense_experts = True
+    rp = Replayer(folder, "float32", 256, page_size=page, device="cpu", ops=ops, max_num_seqs=2)
+    nc.plain_logits(cfg, tensors, tokens, "float32").check(nc.feed(rp, "a", tokens, [17, 2]), "all experts as one matrix")
+
+
 # ---------------------------------------------------------------- one mechanism at a time
 
 def _one_layer(layer, **kw):
@@ -285,8 +298,8 @@ def test_small_kernels_against_the_plain_functions(backend):
         held = rnd(H, dk, dv)
         for delta in (False, True):
             state_all = torch.zeros(4, H * dk * dv + 5)
-            state = state_all[:, 2:2 + H * dk * dv].unflatten(1, (H, dk, dv))
-            state[3], state[0] = held, 5.0
+            state = state_all[:, 2:2 + H * dk * dv].unflatten(1, (H, dv, dk))      # the kernels keep S^T
+            state[3], state[0] = held.transpose(1, 2), 5.0
             want, new_state, at = torch.zeros(T, H, dv, dtype=torch.float64), {}, 0
             for n, slot, fresh in zip(lens, slots, (True, False, True)):
                 S = torch.zeros(H, dk, dv, dtype=torch.float64) if fresh else held.double().clone()
@@ -305,7 +318,7 @@ def test_small_kernels_against_the_plain_functions(backend):
                 new_state[slot] = S
                 at += n
             sd = state_all.to(dev)
-            sv = sd[:, 2:2 + H * dk * dv].unflatten(1, (H, dk, dv))
+            sv = sd[:, 2:2 + H * dk * dv].unflatten(1, (H, dv, dk))
             wd = wide.to(dev)
             how = (dict(beta_logits=wd[:, 1 + H * dv:1 + H * dv + H], decay_logits=wd[:, 1 + H * dv + H:1 + H * dv + 2 * H],
                         decay_rate=rate.to(dev), decay_bias=bias.to(dev)) if delta else dict(decay=decay.to(dev)))
@@ -314,7 +327,7 @@ def test_small_kernels_against_the_plain_functions(backend):
             scale = float(want.abs().max())
             close(got, want.flatten(1), atol=2e-5 * scale, rtol=1e-4)
             for slot, S in new_state.items():
-                close(sv[slot], S, atol=2e-5 * float(S.abs().max()), rtol=1e-4)
+                close(sv[slot], S.transpose(1, 2), atol=2e-5 * float(S.abs().max()), rtol=1e-4)
             assert torch.equal(sd.cpu()[2], state_all[2]) and torch.equal(sd.cpu()[:, :2], state_all[:, :2]), "the state's neighbours changed"
     # the router with a bias that decides the choice, and gated experts
     for T, dim in ((1, 64), (7, 42), (300, 128)):

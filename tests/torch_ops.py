@@ -210,9 +210,14 @@ class TorchOps:
     def moe_prefers_dense(self, n_tokens, top, n_experts, dtype):
         return self.dense_experts
 
-    def moe_dense_hidden(self, x, chosen, weights, gate, w_up_all, *, n_experts, hidden, activation):
+    def moe_dense_hidden(self, x, chosen, weights, gate, w_up_all, *, n_experts, hidden, activation, gated=False):
         T = x.shape[0]
-        u = self._act(x.float() @ w_up_all.float().t(), activation)
+        u = x.float() @ w_up_all.float().t()
+        if gated:            # an expert's columns are [gate | up]
+            u = u.view(T, n_experts, 2, hidden)
+            u = (self._act(u[:, :, 0], activation) * u[:, :, 1]).reshape(T, n_experts * hidden)
+        else:
+            u = self._act(u, activation)
         scale = torch.zeros((T, n_experts), dtype=torch.float32, device=x.device)
         scale.scatter_(1, chosen.long(), weights)
         cols = scale.repeat_interleave(hidden, dim=1)
@@ -310,9 +315,9 @@ class TorchOps:
 
     def linear_recurrence(self, q, k, v, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, decay=None,
                           beta_logits=None, decay_logits=None, decay_rate=None, decay_bias=None):
-        """state [slots, H, dk, dv] float32; q, k float32 [T, G * dk] (G heads shared by H / G value heads each), v [T, H * dv].
+        """state [slots, H, dv, dk] float32 (S transposed: a column's keys side by side); q, k float32 [T, G * dk] (G heads shared by H / G value heads each), v [T, H * dv].
         decay: S = decay_h S + k v^T.  Otherwise the gated delta rule: S = g S; u = beta (v - S^T k); S += k u^T.  o = S^T q."""
-        H, dk, dv = state.shape[1:]
+        H, dv, dk = state.shape[1:]
         G = q.shape[1] // dk
         T = q.shape[0]
         qh, kh = q.view(T, G, dk).float(), k.view(T, G, dk).float()
@@ -324,7 +329,7 @@ class TorchOps:
         qs = q_start.tolist()
         for b in range(n_seqs):
             slot = int(state_slot[b])
-            S = torch.zeros((H, dk, dv)) if int(fresh[b]) else state[slot].clone()
+            S = torch.zeros((H, dk, dv)) if int(fresh[b]) else state[slot].transpose(1, 2).clone()
             for t in range(qs[b], qs[b + 1]):
                 kt = kh[t].repeat_interleave(H // G, dim=0)
                 qt = qh[t].repeat_interleave(H // G, dim=0)
@@ -335,7 +340,7 @@ class TorchOps:
                     u = beta[t][:, None] * (vh[t] - torch.einsum("hkv,hk->hv", S, kt))
                     S = S + kt[:, :, None] * u[:, None, :]
                 out[t] = torch.einsum("hkv,hk->hv", S, qt)
-            state[slot] = S
+            state[slot] = S.transpose(1, 2)
         return out.flatten(1)
 
     def head_norm_gate(self, o, gate, weight, eps, *, head_dim, out_dtype):

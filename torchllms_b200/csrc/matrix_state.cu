@@ -196,7 +196,6 @@ __global__ void __launch_bounds__(NT) head_norm_gate_kernel(const HeadNormParams
 
 
 constexpr int RC_TOKENS = 16;      // tokens fetched into shared memory at a time
-constexpr int RC_COLS = 32;        // columns of the value size that a CTA owns (8 per warp)
 
 struct RecurrenceParams {
     const float* q;          // [T][G * dk]
@@ -208,7 +207,7 @@ struct RecurrenceParams {
     long long ldg;
     const float* decay;      // [H]: the fixed decay, or (delta rule) exp(A_log)
     const float* decay_bias; // [H] (delta rule)
-    float* state;            // [slots] rows of pitch state_pitch, each [H][dk][dv]
+    float* state;            // [slots] rows of pitch state_pitch, each [H][dv][dk]: a column's keys lie side by side
     long long state_pitch;
     const int* q_start;
     const int* state_slot;
@@ -217,92 +216,165 @@ struct RecurrenceParams {
     int H, G, dk, dv;
 };
 
-// A CTA per (32 columns, head, request), 4 warps of 8 columns each; a warp's lanes are 8 columns x 4 slices of the
-// key size: lane (jj, s) keeps S[s R + r][j] for r < R in registers (4 R >= dk; rows past dk stay zero).  q and k of a
-// few tokens lie in shared memory in rows of 4 R floats, zeros past dk, so a lane reads its slice four floats at a
-// time and nothing in the loop over tokens asks where dk ends.  Sums over the key size run as four chains and end
-// with two shuffles.
-template <int R, bool DELTA, typename TV>
+// A CTA of 4 warps per (4 * 32 / KS columns, head, request); a warp's lanes are 32 / KS columns x KS slices of the key
+// size: lane (jj, s) keeps S[s R + r][j] for r < R in registers (KS R >= dk; rows past dk stay zero).  The state is
+// stored with a column's keys side by side, so a lane's slice is one run of R floats.  q and k of 16 tokens lie in
+// shared memory, a slice's R floats followed by 4 unused ones (slices then start in different banks), zeros past
+// dk, so a lane reads its slice four floats at a time and nothing in the loop over tokens asks where dk ends; the
+// next 16 tokens are on their way from global memory into registers meanwhile.  The more slices, the more warps a
+// head gives and the shorter a lane's chain per token, at one more shuffle per doubling.
+//
+// Both sums over the key size that a token needs are taken from the state as the token finds it, in one pass and one
+// round of shuffles, because the state it leaves differs by a rank-one term whose share is known beforehand:
+//     decay:  o = S_t^T q = d (S^T q) + v (k . q)
+//     delta:  S^T k and S^T q of the decayed state are g (S^T k) and g (S^T q);  u = beta (v - g S^T k);
+//             o = g (S^T q) + u (k . q)
+// with S the state before the token and k . q taken once per token when its rows arrive.  That leaves one
+// dependent chain per token (the update of S) instead of two reductions one after the other.
+template <int R, int KS, bool DELTA, typename TV>
 __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceParams p) {
     extern __shared__ __align__(16) float smem[];
     grid_launch_dependents();
     grid_dependency_wait();
-    constexpr int PITCH = 4 * R;
+    constexpr int SLOT = R + 4;                          // a slice in shared memory
+    constexpr int PITCH = KS * SLOT;
+    constexpr int COLS = 4 * (32 / KS);                  // columns of a CTA
+    constexpr int XN = (PITCH + 31) / 32;                // places of a row that a lane brings
+    constexpr int TPW = RC_TOKENS / (NT / 32);           // tokens of the 16 that a warp brings
+    constexpr int V_EACH = (RC_TOKENS * COLS + NT - 1) / NT;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int jj = lane & 7, s = lane >> 3;
+    const int s = lane & (KS - 1), jj = lane / KS;
     const int h = blockIdx.y, b = blockIdx.z;
-    const int jl = warp * 8 + jj, j = blockIdx.x * RC_COLS + jl;
+    const int jl = warp * (32 / KS) + jj, j = blockIdx.x * COLS + jl;
     const bool live = j < p.dv;
     const int g = h / (p.H / p.G);
     const int start = p.q_start[b], len = p.q_start[b + 1] - start;
     if (len <= 0) return;
     float* sq = smem;                                   // [RC_TOKENS][PITCH]
     float* sk = sq + RC_TOKENS * PITCH;                 // [RC_TOKENS][PITCH]
-    float* sv = sk + RC_TOKENS * PITCH;                 // [RC_TOKENS][RC_COLS]
-    float* sg = sv + RC_TOKENS * RC_COLS;               // [RC_TOKENS]: the token's decay
+    float* sv = sk + RC_TOKENS * PITCH;                 // [RC_TOKENS][COLS]
+    float* sg = sv + RC_TOKENS * COLS;                  // [RC_TOKENS]: the token's decay
     float* sb = sg + RC_TOKENS;                         // [RC_TOKENS]: the token's beta
-    float* st = p.state + (size_t)p.state_slot[b] * p.state_pitch + (size_t)h * p.dk * p.dv;
+    float* skq = sb + RC_TOKENS;                        // [RC_TOKENS]: k . q
+    float* st = p.state + (size_t)p.state_slot[b] * p.state_pitch + ((size_t)h * p.dv + (live ? j : 0)) * p.dk;
     float S[R];
     const bool fresh = p.fresh[b] != 0;
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int i = s * R + r;
-        S[r] = (!fresh && live && i < p.dk) ? st[(size_t)i * p.dv + j] : 0.f;
+        S[r] = (!fresh && live && i < p.dk) ? st[i] : 0.f;
     }
     const float fixed = DELTA ? 0.f : p.decay[h];
+    const float rate = DELTA ? p.decay[h] : 0.f, dbias = DELTA ? p.decay_bias[h] : 0.f;
     const TV* v = reinterpret_cast<const TV*>(p.v);
     const int qk_row = p.G * p.dk;
-    for (int t0 = 0; t0 < len; t0 += RC_TOKENS) {
+    // a warp brings whole rows (tokens warp, warp + 4, ...), a lane the places lane, lane + 32, ... of each: which
+    // coordinate of the head a place holds (-1: the unused floats behind a slice, and what lies past dk) is the same
+    // for every token
+    int coord[XN];
+#pragma unroll
+    for (int it = 0; it < XN; ++it) {
+        const int x = lane + 32 * it, sl = x / SLOT, r = x - sl * SLOT, d = sl * R + r;
+        coord[it] = (x < PITCH && r < R && d < p.dk) ? d : -1;
+    }
+    float fq[TPW * XN], fk[TPW * XN], fv[V_EACH], fa = 0.f, fb = 0.f;
+    // the rows of the 16 tokens from t0 on, into registers (zeros past the portion's end)
+    auto fetch = [&](int t0) {
         const int n = min(len - t0, RC_TOKENS);
-        __syncthreads();                                // the tokens before have been used
-        for (int e = threadIdx.x; e < n * PITCH; e += NT) {
-            const int tt = e / PITCH, d = e - tt * PITCH;
-            const size_t at = (size_t)(start + t0 + tt) * qk_row + (size_t)g * p.dk + d;
-            sq[e] = d < p.dk ? p.q[at] : 0.f;
-            sk[e] = d < p.dk ? p.k[at] : 0.f;
+#pragma unroll
+        for (int w = 0; w < TPW; ++w) {
+            const int tt = warp + (NT / 32) * w;
+            const size_t row = (size_t)(start + t0 + tt) * qk_row + (size_t)g * p.dk;
+#pragma unroll
+            for (int it = 0; it < XN; ++it) {
+                const bool in = tt < n && coord[it] >= 0;
+                fq[w * XN + it] = in ? p.q[row + coord[it]] : 0.f;
+                fk[w * XN + it] = in ? p.k[row + coord[it]] : 0.f;
+            }
         }
-        for (int e = threadIdx.x; e < n * RC_COLS; e += NT) {
-            const int tt = e / RC_COLS, c = e - tt * RC_COLS, col = blockIdx.x * RC_COLS + c;
-            sv[e] = col < p.dv ? to_float(v[(size_t)(start + t0 + tt) * p.ldv + (size_t)h * p.dv + col]) : 0.f;
+#pragma unroll
+        for (int i = 0; i < V_EACH; ++i) {
+            const int e = threadIdx.x + i * NT, tt = e / COLS, c = e - tt * COLS, col = blockIdx.x * COLS + c;
+            fv[i] = (tt < n && col < p.dv) ? to_float(v[(size_t)(start + t0 + tt) * p.ldv + (size_t)h * p.dv + col]) : 0.f;
         }
         if (DELTA && threadIdx.x < n) {
             const size_t at = (size_t)(start + t0 + threadIdx.x) * p.ldg + h;
-            const float a = to_float(reinterpret_cast<const TV*>(p.gate)[at]) + p.decay_bias[h];
+            fa = to_float(reinterpret_cast<const TV*>(p.gate)[at]);
+            fb = to_float(reinterpret_cast<const TV*>(p.beta)[at]);
+        }
+    };
+    fetch(0);
+    for (int t0 = 0; t0 < len; t0 += RC_TOKENS) {
+        const int n = min(len - t0, RC_TOKENS);
+        __syncthreads();                                // the tokens before have been used
+#pragma unroll
+        for (int w = 0; w < TPW; ++w) {
+            const int tt = warp + (NT / 32) * w;
+            float acc = 0.f;                            // k . q of the token, from the registers that hold its rows
+#pragma unroll
+            for (int it = 0; it < XN; ++it) {
+                const int x = lane + 32 * it;
+                if (x < PITCH) {
+                    sq[tt * PITCH + x] = fq[w * XN + it];
+                    sk[tt * PITCH + x] = fk[w * XN + it];
+                }
+                acc = fmaf(fq[w * XN + it], fk[w * XN + it], acc);
+            }
+            acc = warp_sum(acc);
+            if (lane == 0) skq[tt] = acc;
+        }
+#pragma unroll
+        for (int i = 0; i < V_EACH; ++i)
+            if (threadIdx.x + i * NT < RC_TOKENS * COLS) sv[threadIdx.x + i * NT] = fv[i];
+        if (DELTA && threadIdx.x < n) {
+            const float a = fa + dbias;
             const float soft = a > 20.f ? a : log1pf(expf(a));
-            sg[threadIdx.x] = expf(-p.decay[h] * soft);
-            sb[threadIdx.x] = 1.f / (1.f + expf(-to_float(reinterpret_cast<const TV*>(p.beta)[at])));
+            sg[threadIdx.x] = expf(-rate * soft);
+            sb[threadIdx.x] = 1.f / (1.f + expf(-fb));
         }
         __syncthreads();
+        if (t0 + RC_TOKENS < len) fetch(t0 + RC_TOKENS);  // in flight while these tokens are walked
         for (int tt = 0; tt < n; ++tt) {
-            const float4* kt = reinterpret_cast<const float4*>(sk + tt * PITCH + s * R);
-            const float4* qt = reinterpret_cast<const float4*>(sq + tt * PITCH + s * R);
-            const float vt = sv[tt * RC_COLS + jl];
+            const float4* kt = reinterpret_cast<const float4*>(sk + tt * PITCH + s * SLOT);
+            const float4* qt = reinterpret_cast<const float4*>(sq + tt * PITCH + s * SLOT);
+            const float vt = sv[tt * COLS + jl], kq = skq[tt];
             float4 kv[R / 4];
+            float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f, o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
 #pragma unroll
-            for (int r = 0; r < R / 4; ++r) kv[r] = kt[r];
-            if (DELTA) {
-                const float gt = sg[tt];
-                float d0 = 0.f, d1 = 0.f, d2 = 0.f, d3 = 0.f;
-#pragma unroll
-                for (int r = 0; r < R / 4; ++r) {
-                    S[4 * r] *= gt; S[4 * r + 1] *= gt; S[4 * r + 2] *= gt; S[4 * r + 3] *= gt;
+            for (int r = 0; r < R / 4; ++r) {
+                kv[r] = kt[r];
+                const float4 qv = qt[r];
+                o0 = fmaf(S[4 * r], qv.x, o0);
+                o1 = fmaf(S[4 * r + 1], qv.y, o1);
+                o2 = fmaf(S[4 * r + 2], qv.z, o2);
+                o3 = fmaf(S[4 * r + 3], qv.w, o3);
+                if (DELTA) {
                     d0 = fmaf(S[4 * r], kv[r].x, d0);
                     d1 = fmaf(S[4 * r + 1], kv[r].y, d1);
                     d2 = fmaf(S[4 * r + 2], kv[r].z, d2);
                     d3 = fmaf(S[4 * r + 3], kv[r].w, d3);
                 }
-                float dot = (d0 + d1) + (d2 + d3);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 8);
-                dot += __shfl_xor_sync(0xffffffffu, dot, 16);
-                const float u = sb[tt] * (vt - dot);
+            }
+            float oq = (o0 + o1) + (o2 + o3), dot = (d0 + d1) + (d2 + d3);
+#pragma unroll
+            for (int off = 1; off < KS; off <<= 1) {
+                oq += __shfl_xor_sync(0xffffffffu, oq, off);
+                if (DELTA) dot += __shfl_xor_sync(0xffffffffu, dot, off);
+            }
+            float o;
+            if (DELTA) {
+                const float gt = sg[tt];
+                const float u = sb[tt] * (vt - gt * dot);
+                o = fmaf(u, kq, gt * oq);
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
-                    S[4 * r] = fmaf(kv[r].x, u, S[4 * r]);
-                    S[4 * r + 1] = fmaf(kv[r].y, u, S[4 * r + 1]);
-                    S[4 * r + 2] = fmaf(kv[r].z, u, S[4 * r + 2]);
-                    S[4 * r + 3] = fmaf(kv[r].w, u, S[4 * r + 3]);
+                    S[4 * r] = fmaf(kv[r].x, u, gt * S[4 * r]);
+                    S[4 * r + 1] = fmaf(kv[r].y, u, gt * S[4 * r + 1]);
+                    S[4 * r + 2] = fmaf(kv[r].z, u, gt * S[4 * r + 2]);
+                    S[4 * r + 3] = fmaf(kv[r].w, u, gt * S[4 * r + 3]);
                 }
             } else {
+                o = fmaf(vt, kq, fixed * oq);
 #pragma unroll
                 for (int r = 0; r < R / 4; ++r) {
                     S[4 * r] = fmaf(fixed, S[4 * r], kv[r].x * vt);
@@ -311,25 +383,13 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
                     S[4 * r + 3] = fmaf(fixed, S[4 * r + 3], kv[r].w * vt);
                 }
             }
-            float o0 = 0.f, o1 = 0.f, o2 = 0.f, o3 = 0.f;
-#pragma unroll
-            for (int r = 0; r < R / 4; ++r) {
-                const float4 qv = qt[r];
-                o0 = fmaf(S[4 * r], qv.x, o0);
-                o1 = fmaf(S[4 * r + 1], qv.y, o1);
-                o2 = fmaf(S[4 * r + 2], qv.z, o2);
-                o3 = fmaf(S[4 * r + 3], qv.w, o3);
-            }
-            float o = (o0 + o1) + (o2 + o3);
-            o += __shfl_xor_sync(0xffffffffu, o, 8);
-            o += __shfl_xor_sync(0xffffffffu, o, 16);
             if (s == 0 && live) p.out[(size_t)(start + t0 + tt) * p.H * p.dv + (size_t)h * p.dv + j] = o;
         }
     }
 #pragma unroll
     for (int r = 0; r < R; ++r) {
         const int i = s * R + r;
-        if (live && i < p.dk) st[(size_t)i * p.dv + j] = S[r];
+        if (live && i < p.dk) st[i] = S[r];
     }
 }
 
@@ -389,7 +449,7 @@ extern "C" int tl_recurrence_prep(const void* x, int in_dtype, long long ldx, fl
 }
 
 // q, k: float32 [n_tokens][qk_heads * dk]; v: rows of pitch ldv, heads * dv columns; state: float32, per slot a row of
-// pitch state_pitch holding [heads][dk][dv]; out: float32 [n_tokens][heads * dv].  delta == 0: decay is [heads], the
+// pitch state_pitch holding [heads][dv][dk] (the matrix of a head with a column's keys side by side); out: float32 [n_tokens][heads * dv].  delta == 0: decay is [heads], the
 // fixed decay.  delta != 0: beta and gate are rows of pitch ldg with `heads` columns (of v's dtype), decay is
 // exp(A_log) per head and decay_bias the bias inside the softplus.
 extern "C" int tl_linear_recurrence(const float* q, const float* k, const void* v, int v_dtype, long long ldv, const void* beta,
@@ -405,17 +465,21 @@ extern "C" int tl_linear_recurrence(const float* q, const float* k, const void* 
     p.q = q; p.k = k; p.v = v; p.ldv = ldv; p.beta = beta; p.gate = gate; p.ldg = ldg; p.decay = decay; p.decay_bias = decay_bias;
     p.state = state; p.state_pitch = state_pitch; p.q_start = q_start; p.state_slot = state_slot; p.fresh = fresh; p.out = out;
     p.H = heads; p.G = qk_heads; p.dk = dk; p.dv = dv;
-    const int need = (dk + 3) / 4;
-    const int rows = need <= 8 ? 8 : need <= 16 ? 16 : need <= 24 ? 24 : need <= 32 ? 32 : need <= 48 ? 48 : 64;   // R of the kernel chosen below
-    const size_t smem = ((size_t)2 * RC_TOKENS * 4 * rows + RC_TOKENS * RC_COLS + 2 * RC_TOKENS) * sizeof(float);
-    const dim3 grid((dv + RC_COLS - 1) / RC_COLS, heads, n_seqs), block(NT);
+    // slices of the key size per column, and a lane's share of it (a multiple of 4)
+    const int ks = dk >= 128 ? 16 : dk > 32 ? 8 : 4;
+    const int share = (dk + ks - 1) / ks;
+    const int rows = share <= 8 ? 8 : share <= 12 ? 12 : 16;
+    const int cols = 4 * (32 / ks);
+    const size_t smem = ((size_t)2 * RC_TOKENS * ks * (rows + 4) + RC_TOKENS * cols + 3 * RC_TOKENS) * sizeof(float);
+    const dim3 grid((dv + cols - 1) / cols, heads, n_seqs), block(NT);
     cudaStream_t s = (cudaStream_t)stream;
-#define TL_REC(R, TV)                                                                                               \
-    (delta ? tl_launch(linear_recurrence_kernel<R, true, TV>, grid, block, smem, s, p)                              \
-           : tl_launch(linear_recurrence_kernel<R, false, TV>, grid, block, smem, s, p))
+#define TL_REC(R, KS, TV)                                                                                           \
+    (delta ? tl_launch(linear_recurrence_kernel<R, KS, true, TV>, grid, block, smem, s, p)                          \
+           : tl_launch(linear_recurrence_kernel<R, KS, false, TV>, grid, block, smem, s, p))
 #define TL_REC_SIZES(TV)                                                                                            \
-    (need <= 8 ? TL_REC(8, TV) : need <= 16 ? TL_REC(16, TV) : need <= 24 ? TL_REC(24, TV) : need <= 32 ? TL_REC(32, TV) \
-     : need <= 48 ? TL_REC(48, TV) : TL_REC(64, TV))
+    (ks == 4 ? TL_REC(8, 4, TV)                                                                                     \
+     : ks == 8 ? (rows == 8 ? TL_REC(8, 8, TV) : rows == 12 ? TL_REC(12, 8, TV) : TL_REC(16, 8, TV))                \
+               : (rows == 8 ? TL_REC(8, 16, TV) : rows == 12 ? TL_REC(12, 16, TV) : TL_REC(16, 16, TV)))
     if (v_dtype == TL_F32) return (int)TL_REC_SIZES(float);
     if (v_dtype == TL_BF16) return (int)TL_REC_SIZES(__nv_bfloat16);
 #undef TL_REC_SIZES

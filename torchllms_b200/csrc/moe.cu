@@ -334,7 +334,7 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 template <typename TI, typename TO>
 __global__ void moe_scale_act_kernel(const TI* __restrict__ u, int splits, long long plane, const int* __restrict__ chosen,
                                      const float* __restrict__ weights, const float* __restrict__ gate, TO* __restrict__ out,
-                                     int n_experts, int hidden, int extra, int top, int act) {
+                                     int n_experts, int hidden, int extra, int top, int act, int gated) {
     extern __shared__ float wexp[];      // [n_experts]: this token's weight per expert
     grid_launch_dependents();
     grid_dependency_wait();
@@ -344,6 +344,25 @@ __global__ void moe_scale_act_kernel(const TI* __restrict__ u, int splits, long 
     if (threadIdx.x < top) wexp[chosen[(size_t)t * top + threadIdx.x]] = weights[(size_t)t * top + threadIdx.x];
     __syncthreads();
     const float g = gate != nullptr ? gate[t] : 1.f;
+    if (gated) {
+        // an expert's columns of u are [gate | up], hidden each; out has hidden columns per expert: act(gate) * up * weight
+        for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
+            const int e = c / hidden, f = c - e * hidden;
+            const float w = wexp[e];
+            float v = 0.f;
+            if (w != 0.f) {
+                const size_t at = (size_t)t * 2 * width + (size_t)e * 2 * hidden + f;
+                float a = 0.f, b = 0.f;
+                for (int sp = 0; sp < splits; ++sp) {
+                    a += to_float(u[(size_t)sp * plane + at]);
+                    b += to_float(u[(size_t)sp * plane + at + hidden]);
+                }
+                v = act_apply(a, act) * b * w;
+            }
+            out[(size_t)t * width + c] = from_float<TO>(v);
+        }
+        return;
+    }
     for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
         const float w = c < n_experts * hidden ? wexp[c / hidden] : g;
         float v = 0.f;
@@ -367,11 +386,14 @@ extern "C" int tl_moe_gather(const void* x, int dtype, const int* order, void* o
     return TL_BAD_DTYPE;
 }
 
-// u: [splits][n_tokens][n_experts * hidden + extra] of in_dtype; out: the same row shape in out_dtype
+// u: [splits][n_tokens][n_experts * hidden + extra] of in_dtype; out: the same row shape in out_dtype.  gated != 0
+// (extra == 0): u is [splits][n_tokens][n_experts * 2 * hidden], an expert's columns [gate | up], and out
+// [n_tokens][n_experts * hidden] holds act(gate) * up * weight.
 extern "C" int tl_moe_scale_act(const void* u, int in_dtype, int splits, long long plane, const int* chosen, const float* weights,
                                 const float* gate, void* out, int out_dtype, int n_tokens, int n_experts, int hidden, int extra,
-                                int top, int act, void* stream) {
+                                int top, int act, int gated, void* stream) {
     if (n_tokens <= 0) return TL_OK;
+    if (gated && extra != 0) return TL_BAD_SIZE;
     if (n_experts <= 0 || hidden <= 0 || extra < 0 || top <= 0 || top > 1024 || splits < 1 || act < -1 || act > 2) return TL_BAD_SIZE;
     const size_t smem = (size_t)n_experts * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
@@ -382,7 +404,7 @@ extern "C" int tl_moe_scale_act(const void* u, int in_dtype, int splits, long lo
     cudaStream_t s = (cudaStream_t)stream;
 #define TL_MOE_SA(TI, TO)                                                                                             \
     tl_launch(moe_scale_act_kernel<TI, TO>, grid, block, smem, s, (const TI*)u, splits, plane, chosen, weights, gate, (TO*)out, \
-              n_experts, hidden, extra, top, act)
+              n_experts, hidden, extra, top, act, gated)
     if (in_dtype == TL_F32 && out_dtype == TL_F32) return (int)TL_MOE_SA(float, float);
     if (in_dtype == TL_F32 && out_dtype == TL_BF16) return (int)TL_MOE_SA(float, __nv_bfloat16);
     if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return (int)TL_MOE_SA(__nv_bfloat16, __nv_bfloat16);

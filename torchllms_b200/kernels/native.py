@@ -738,12 +738,13 @@ class NativeOps:
         ``S <- g S; u = beta (v - S^T k); S <- S + k u^T`` with ``beta = sigmoid(beta_logits)`` and
         ``g = exp(-decay_rate softplus(decay_logits + decay_bias))`` (logits ``[T, H]``, the rest float32 ``[H]``).
         ``q``, ``k``: float32 ``[T, G * dk]``, ``G`` heads each shared by ``H / G`` value heads; ``v``: ``[T, H * dv]``;
-        ``state``: ``[slots, H, dk, dv]``, read (zeros where ``fresh``) and left updated.  Returns float32 ``[T, H * dv]``."""
+        ``state``: ``[slots, H, dv, dk]`` (a head's matrix with a column's keys side by side), read (zeros where
+        ``fresh``) and left updated.  Returns float32 ``[T, H * dv]``."""
         _cuda_contig(q, "q", torch.float32)
         _cuda_contig(k, "k", torch.float32)
         ldv = self._rows_view(v, "v")
-        _need(state.dim() == 4, "state must be [slots, heads, dk, dv]")
-        H, dk, dv = state.shape[1:]
+        _need(state.dim() == 4, "state must be [slots, heads, dv, dk]")
+        H, dv, dk = state.shape[1:]
         pitch = self._state_view(state, H * dk * dv, "recurrence state")
         T = q.shape[0]
         _need(q.dim() == 2 and q.shape == k.shape and q.shape[1] % dk == 0 and v.shape == (T, H * dv), "linear_recurrence: sizes")
@@ -983,20 +984,22 @@ class NativeOps:
 
     @_timed
     def moe_dense_hidden(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, gate: Optional[torch.Tensor],
-                         w_up_all: torch.Tensor, *, n_experts: int, hidden: int, activation: str) -> torch.Tensor:
+                         w_up_all: torch.Tensor, *, n_experts: int, hidden: int, activation: str, gated: bool = False) -> torch.Tensor:
         """The hidden rows of *all* experts for a few tokens: ``w_up_all`` is every expert's up matrix
         stacked (``[E * hidden + extra, dim]``, the ``extra`` rows a shared expert's); returns
         ``[T, E * hidden + extra]`` with ``act(up_e x[t]) * weight(t, e)`` in expert ``e``'s columns (zero
-        where the token did not choose it) and ``act(.) * gate[t]`` in the extra ones.  The product of
+        where the token did not choose it) and ``act(.) * gate[t]`` in the extra ones.  With ``gated`` an expert's rows
+        of ``w_up_all`` are ``[gate; up]`` (``2 * hidden``, no extra rows) and its ``hidden`` columns of the result hold
+        ``act(gate_e x) * (up_e x) * weight``.  The product of
         that with the experts' down matrices side by side (``[dim, E * hidden + extra]``) is the layer's
         output."""
         _cuda_contig(chosen, "chosen", torch.int32)
         _cuda_contig(weights, "weights", torch.float32)
         _need(activation in self._ACTS, f"unknown activation {activation!r}")
         T, top = chosen.shape
-        width = w_up_all.shape[0]
+        width = w_up_all.shape[0] // (2 if gated else 1)
         extra = width - n_experts * hidden
-        _need(extra >= 0 and x.shape[0] == T and weights.shape == chosen.shape, "moe_dense_hidden: shapes disagree")
+        _need((not gated or extra == 0) and extra >= 0 and x.shape[0] == T and weights.shape == chosen.shape, "moe_dense_hidden: shapes disagree")
         if gate is not None:
             _cuda_contig(gate, "shared gate", torch.float32)
         u = self.linear(x, w_up_all, partials_ok=True)
@@ -1004,7 +1007,7 @@ class NativeOps:
         out = torch.empty((T, width), dtype=x.dtype, device=x.device)
         rc = self._lib("moe").tl_moe_scale_act(_ptr(u), _DT[u.dtype], splits, ctypes.c_longlong(u.stride(0) if splits > 1 else 0),
                                               _ptr(chosen), _ptr(weights), _ptr(gate), _ptr(out), _DT[x.dtype], T, n_experts, hidden,
-                                              extra, top, self._ACTS[activation], _stream())
+                                              extra, top, self._ACTS[activation], 1 if gated else 0, _stream())
         _check(rc, "moe_scale_act")
         self.launches += 1
         return out

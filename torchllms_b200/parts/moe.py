@@ -126,10 +126,10 @@ class RoutedExperts(FeedForward):
         chosen, weights, gate = ops.moe_route(x, self.w_router, self.correction, n_experts=self.n_experts, top=self.top,
                                               scale=self.router_scale, renormalize=self.renormalize,
                                               shared_gate=self.shared_gate, logit_bias=self.logit_bias)
-        if not self.gated and ops.moe_prefers_dense(x.shape[0], self.top, self.n_experts, x.dtype):
+        if ops.moe_prefers_dense(x.shape[0], self.top, self.n_experts, x.dtype):
             # few tokens that touch most experts between them: every expert (and the shared one) as one
             # matrix each way, the rows of experts a token did not choose multiplied by zero
-            u = ops.moe_dense_hidden(x, chosen, weights, gate, self.w_up_all, n_experts=self.n_experts, hidden=self.hidden,
+            u = ops.moe_dense_hidden(x, chosen, weights, gate, self.w_up_all, n_experts=self.n_experts, hidden=self.hidden, gated=self.gated,
                                      activation=self.activation)
             return PendingProduct(u, self.w_down_all)
         shared = None

@@ -105,7 +105,7 @@ class Retention(Mixer):
         self.wo: Optional[torch.Tensor] = None
 
     def state_need(self) -> StateNeed:
-        return StateNeed((self.n_heads, self.head_dim, self.v_head_dim), torch.float32)
+        return StateNeed((self.n_heads, self.v_head_dim, self.head_dim), torch.float32)      # S^T: a column's keys side by side
 
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
         d = self.dim
@@ -164,7 +164,7 @@ class GatedDelta(Mixer):
         self.n_qk, self.n_v = self.n_qk_heads * self.head_dim, self.n_heads * self.v_head_dim
         self.n_conv = 2 * self.n_qk + self.n_v
         self._need = join_states([("conv", StateNeed((self.taps - 1, self.n_conv)) if self.taps > 1 else None),
-                                  ("matrix", StateNeed((self.n_heads, self.head_dim, self.v_head_dim)))])
+                                  ("matrix", StateNeed((self.n_heads, self.v_head_dim, self.head_dim)))])      # S^T per head
         self.w_in = self.w_conv = self.decay_rate = self.decay_bias = self.norm_w = self.wo = None
 
     def state_need(self) -> StateNeed:
