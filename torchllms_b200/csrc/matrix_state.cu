@@ -465,10 +465,17 @@ extern "C" int tl_linear_recurrence(const float* q, const float* k, const void* 
     p.q = q; p.k = k; p.v = v; p.ldv = ldv; p.beta = beta; p.gate = gate; p.ldg = ldg; p.decay = decay; p.decay_bias = decay_bias;
     p.state = state; p.state_pitch = state_pitch; p.q_start = q_start; p.state_slot = state_slot; p.fresh = fresh; p.out = out;
     p.H = heads; p.G = qk_heads; p.dk = dk; p.dv = dv;
-    // slices of the key size per column, and a lane's share of it (a multiple of 4)
-    const int ks = dk >= 128 ? 16 : dk > 32 ? 8 : 4;
+    // slices of the key size per column (TORCHLLMS_B200_REC_SLICES=4|8|16 overrides the choice, for comparisons), and a
+    // lane's share of it (a multiple of 4)
+    static int forced = -1;
+    if (forced < 0) {
+        const char* e = getenv("TORCHLLMS_B200_REC_SLICES");
+        forced = e != nullptr ? atoi(e) : 0;
+    }
+    int ks = dk > 128 ? 16 : dk > 32 ? 8 : 4;
+    if ((forced == 4 && dk <= 128) || (forced == 8 && dk <= 128) || forced == 16) ks = forced;
     const int share = (dk + ks - 1) / ks;
-    const int rows = share <= 8 ? 8 : share <= 12 ? 12 : 16;
+    const int rows = share <= 8 ? 8 : share <= 12 ? 12 : share <= 16 ? 16 : share <= 24 ? 24 : 32;
     const int cols = 4 * (32 / ks);
     const size_t smem = ((size_t)2 * RC_TOKENS * ks * (rows + 4) + RC_TOKENS * cols + 3 * RC_TOKENS) * sizeof(float);
     const dim3 grid((dv + cols - 1) / cols, heads, n_seqs), block(NT);
@@ -477,7 +484,7 @@ extern "C" int tl_linear_recurrence(const float* q, const float* k, const void* 
     (delta ? tl_launch(linear_recurrence_kernel<R, KS, true, TV>, grid, block, smem, s, p)                          \
            : tl_launch(linear_recurrence_kernel<R, KS, false, TV>, grid, block, smem, s, p))
 #define TL_REC_SIZES(TV)                                                                                            \
-    (ks == 4 ? TL_REC(8, 4, TV)                                                                                     \
+    (ks == 4 ? (rows == 8 ? TL_REC(8, 4, TV) : rows <= 16 ? TL_REC(16, 4, TV) : rows == 24 ? TL_REC(24, 4, TV) : TL_REC(32, 4, TV)) \
      : ks == 8 ? (rows == 8 ? TL_REC(8, 8, TV) : rows == 12 ? TL_REC(12, 8, TV) : TL_REC(16, 8, TV))                \
                : (rows == 8 ? TL_REC(8, 16, TV) : rows == 12 ? TL_REC(12, 16, TV) : TL_REC(16, 16, TV)))
     if (v_dtype == TL_F32) return (int)TL_REC_SIZES(float);
