@@ -230,15 +230,26 @@ def test_small_kernels_against_the_plain_functions(backend):
                               plain=(c.to(dev), d.to(dev)), out_dtype=dtype)
         close(hd, want, atol=2e-5, rtol=2e-5)
         close(rows, want)
+        # the same with a normed and a plain term that arrive as partial sums of a split-K product
+        pa, pc = rnd(3, T, dim), rnd(2, T, dim)
+        want = h.double() + 0.5 * (plain.rms(pa.double().sum(0), 1e-5) * wa + plain.rms(b.double(), 1e-5) * wb) + pc.double().sum(0)
+        hd = h.clone().to(dev)
+        ops.stream_add(hd, normed=((pa.to(dev), wa.to(dev)), (b.to(dev), wb.to(dev))), coef=0.5, eps=1e-5, plain=(pc.to(dev),), out_dtype=dtype)
+        close(hd, want, atol=3e-5, rtol=3e-5)
+        close(ops.sum_partials(pa.to(dev), dtype), pa.double().sum(0))
         # PolyNorm
         z, coef = rnd(T, dim).to(dtype), torch.tensor([0.9, -0.4, 0.3, 0.2])
         zd = z.double()
         want = 0.9 * plain.rms(zd, 1e-6) - 0.4 * plain.rms(zd ** 2, 1e-6) + 0.3 * plain.rms(zd ** 3, 1e-6) + 0.2
         close(ops.polynorm(z.to(dev), coef.to(dev), 1e-6, dtype), want)
+        zp = torch.stack([0.25 * z.float(), 0.75 * z.float()])
+        close(ops.polynorm(zp.to(dev), coef.to(dev), 1e-6, dtype), want)
         # the side input's gate
         s = 5 if dim % 4 else 24
         u, table, ids = rnd(T, s).to(dtype), rnd(11, s).to(dtype), torch.randint(0, 11, (T,), generator=g)
         close(ops.side_gate(u.to(dev), i32(ids.tolist()), table.to(dev), dtype), plain.gelu_tanh(u.double()) * table.double()[ids])
+        up = torch.stack([0.5 * u.float(), 0.25 * u.float(), 0.25 * u.float()])
+        close(ops.side_gate(up.to(dev), i32(ids.tolist()), table.to(dev), dtype), plain.gelu_tanh(u.double()) * table.double()[ids])
         # the head norm with its gate: heads inside a wider row of gates
         H, hd_ = (3, 10) if dim % 4 else (4, 32)
         o, wide, w = rnd(T, H * hd_), rnd(T, H * hd_ + 6).to(dtype), rnd(hd_)
@@ -333,7 +344,7 @@ def test_small_kernels_against_the_plain_functions(backend):
     for T, dim in ((1, 64), (7, 42), (300, 128)):
         E, top, ff = 7, 3, 24
         x = rnd(T, dim).to(dtype)
-        W = {"m.router": 0.5 * rnd(E, dim), "m.router.b": torch.tensor([0.0, 30.0, 0.0, -30.0, 0.0, 0.0, 0.0])}
+        W = {"m.router": 2.0 * rnd(E, dim) / dim ** 0.5, "m.router.b": torch.tensor([0.0, 30.0, 0.0, -30.0, 0.0, 0.0, 0.0])}
         for e in range(E):
             W.update({f"m.e{e}.gate": (rnd(ff, dim) * 2 / dim ** 0.5).to(dtype).float(), f"m.e{e}.up": (rnd(ff, dim) * 2 / dim ** 0.5).to(dtype).float(),
                       f"m.e{e}.down": (rnd(dim, ff) / ff ** 0.5).to(dtype).float()})

@@ -271,7 +271,7 @@ class TorchOps:
     def stream_add(self, h, *, normed, coef, eps, plain, out_dtype):
         """h += coef * sum_i t_i / sqrt(mean(t_i^2) + eps) * w_i + sum_j p_j (in place, float32); the new rows in out_dtype."""
         for t, w in normed:
-            t = t.float()
+            t = t.float().sum(0) if t.dim() == 3 else t.float()
             h += np.float32(coef) * (t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps) * w)
         for p in plain:
             h += p.float().sum(0) if p.dim() == 3 else p.float()
@@ -354,7 +354,11 @@ class TorchOps:
 
     def side_gate(self, u, token_ids, table, out_dtype):
         """gelu_tanh(u) * table[token]."""
-        return (self._act(u.float(), "gelu_tanh") * table[token_ids.long()].float()).to(out_dtype)
+        u = u.float().sum(0) if u.dim() == 3 else u.float()
+        return (self._act(u, "gelu_tanh") * table[token_ids.long()].float()).to(out_dtype)
+
+    def sum_partials(self, parts, out_dtype):
+        return parts.float().sum(0).to(out_dtype)
 
     def polynorm(self, z, coef, eps, out_dtype):
         """a N(z) + b N(z^2) + c N(z^3) + e with N(y) = y / sqrt(mean(y^2) + eps) over a row; coef = (a, b, c, e)."""

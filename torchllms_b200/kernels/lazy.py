@@ -70,13 +70,13 @@ class RowScaled:
 
 @dataclass
 class NormedSum:
-    terms: tuple             # ((tensor [T, dim], weight float32 [dim]), ...)
+    terms: tuple             # ((tensor [T, dim] or float32 partial sums [splits, T, dim], weight float32 [dim]), ...)
     coef: float
     eps: float
 
     def take(self, ops, out_dtype: torch.dtype):
         """The sum as a tensor (a kernel of its own: the sum onto a stream of zeros)."""
         t = self.terms[0][0]
-        h = torch.zeros(t.shape, dtype=torch.float32, device=t.device)
+        h = torch.zeros(t.shape[-2:], dtype=torch.float32, device=t.device)
         out = ops.stream_add(h, normed=self.terms, coef=self.coef, eps=self.eps, plain=(), out_dtype=out_dtype)
         return out

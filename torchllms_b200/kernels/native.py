@@ -797,29 +797,50 @@ class NativeOps:
     def stream_add(self, h: torch.Tensor, *, normed, coef: float, eps: float, plain, out_dtype: torch.dtype) -> torch.Tensor:
         """``h += coef * sum_i t_i / sqrt(mean(t_i^2) + eps) * w_i + sum_j p_j`` in place (float32), one kernel:
         ``normed`` is up to two ``(t_i, w_i)`` (``[T, dim]``, float32 ``[dim]``), ``plain`` up to three ``[T, dim]``
-        tensors.  Returns the new stream in ``out_dtype`` (``h`` itself for float32)."""
+        tensors; any of them may be float32 partial sums ``[splits, T, dim]`` of a split-K product.  Returns the new stream in ``out_dtype`` (``h`` itself for float32)."""
         _cuda_contig(h, "residual stream", torch.float32)
         _need(h.dim() == 2 and len(normed) <= 2 and len(plain) <= 3, "stream_add: at most two normed and three plain terms")
         _need(out_dtype in _DT, f"stream_add: output dtype {out_dtype} unsupported")
-        for t, w in normed:
-            _cuda_contig(t, "normed term")
+        def term(t, name):
+            """(plane count, planes' distance): a term is [T, dim] or float32 partial sums [splits, T, dim]"""
+            _cuda_contig(t, name)
+            _need(t.dtype in _DT and t.shape[-2:] == h.shape and (t.dim() == 2 or (t.dim() == 3 and t.dtype == torch.float32)),
+                  f"a {name} has the stream's shape, or is float32 partial sums of it")
+            return (t.shape[0], t.stride(0)) if t.dim() == 3 else (1, 0)
+        for _t, w in normed:
             _cuda_contig(w, "norm weight", torch.float32)
-            _need(t.shape == h.shape and t.dtype in _DT and w.numel() == h.shape[1], "a normed term has the stream's shape")
-        for t in plain:
-            _cuda_contig(t, "plain term")
-            _need(t.shape == h.shape and t.dtype in _DT, "a plain term has the stream's shape")
+            _need(w.numel() == h.shape[1], "a norm weight has the stream's width")
         n, m = len(normed), len(plain)
+        n_how = [term(t, "normed term") for t, _w in normed]
+        p_how = [term(t, "plain term") for t in plain]
         np_ = (ctypes.c_void_p * 2)(*[t.data_ptr() for t, _w in normed])
         nd = (ctypes.c_int * 2)(*[_DT[t.dtype] for t, _w in normed])
+        ns = (ctypes.c_int * 2)(*[a for a, _b in n_how])
+        npl = (ctypes.c_longlong * 2)(*[b for _a, b in n_how])
         nw = (ctypes.c_void_p * 2)(*[w.data_ptr() for _t, w in normed])
         pp = (ctypes.c_void_p * 3)(*[t.data_ptr() for t in plain])
         pd = (ctypes.c_int * 3)(*[_DT[t.dtype] for t in plain])
+        ps = (ctypes.c_int * 3)(*[a for a, _b in p_how])
+        ppl = (ctypes.c_longlong * 3)(*[b for _a, b in p_how])
         rows = None if out_dtype == torch.float32 else torch.empty(h.shape, dtype=out_dtype, device=h.device)
-        rc = self._lib("stream_sum").tl_stream_add(_ptr(h), np_, nd, nw, n, pp, pd, m, ctypes.c_float(coef), ctypes.c_float(eps),
+        rc = self._lib("stream_sum").tl_stream_add(_ptr(h), np_, nd, ns, npl, nw, n, pp, pd, ps, ppl, m, ctypes.c_float(coef), ctypes.c_float(eps),
                                                   _ptr(rows), h.shape[0], h.shape[1], _stream())
         _check(rc, "stream_add")
         self.launches += 1
         return h if rows is None else rows
+
+    @_timed
+    def sum_partials(self, parts: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+        """Float32 partial sums ``[splits, ...]`` of a split-K product added up and rounded once, for readers that take
+        no partial sums."""
+        _cuda_contig(parts, "partial sums", torch.float32)
+        _need(parts.dim() >= 2 and out_dtype in _DT, "sum_partials: [splits, ...] float32 to float32 or bfloat16")
+        out = torch.empty(parts.shape[1:], dtype=out_dtype, device=parts.device)
+        rc = self._lib("stream_sum").tl_sum_partials(_ptr(parts), parts.shape[0], ctypes.c_longlong(parts.stride(0)), _ptr(out),
+                                                    _DT[out_dtype], ctypes.c_longlong(out.numel()), _stream())
+        _check(rc, "sum_partials")
+        self.launches += 1
+        return out
 
     @_timed
     def polynorm(self, z: torch.Tensor, coef: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
@@ -827,25 +848,32 @@ class NativeOps:
         element; ``coef`` is float32 ``(a, b, c, e)``."""
         _cuda_contig(z, "polynorm input")
         _cuda_contig(coef, "polynorm coefficients", torch.float32)
-        _need(z.dim() == 2 and z.dtype in _DT and coef.numel() == 4, "polynorm: z [T, width], four coefficients")
+        _need(z.dim() in (2, 3) and z.dtype in _DT and coef.numel() == 4, "polynorm: z [T, width] or partial sums of it, four coefficients")
+        splits = z.shape[0] if z.dim() == 3 else 1
+        _need(splits == 1 or z.dtype == torch.float32, "partial sums must be float32")
         _need(out_dtype in _DT and (out_dtype == z.dtype or z.dtype == torch.float32), "polynorm cannot widen bfloat16 input")
-        out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
-        rc = self._lib("stream_sum").tl_polynorm(_ptr(z), _DT[z.dtype], _ptr(coef), _ptr(out), _DT[out_dtype], z.shape[0], z.shape[1],
-                                                ctypes.c_float(eps), _stream())
+        out = torch.empty(z.shape[-2:], dtype=out_dtype, device=z.device)
+        rc = self._lib("stream_sum").tl_polynorm(_ptr(z), _DT[z.dtype], splits, ctypes.c_longlong(z.stride(0) if splits > 1 else 0),
+                                                _ptr(coef), _ptr(out), _DT[out_dtype], z.shape[-2], z.shape[-1], ctypes.c_float(eps),
+                                                _stream())
         _check(rc, "polynorm")
         self.launches += 1
         return out
 
     @_timed
     def side_gate(self, u: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
-        """``gelu_tanh(u) * table[token]``: ``u`` ``[T, s]``, ``table`` ``[vocab, s]``, both of ``out_dtype``."""
-        _cuda_contig(u, "side gate input", out_dtype)
+        """``gelu_tanh(u) * table[token]``: ``u`` ``[T, s]`` (or float32 partial sums ``[splits, T, s]``), ``table``
+        ``[vocab, s]`` of ``out_dtype``."""
+        _cuda_contig(u, "side gate input")
         _cuda_contig(table, "side table", out_dtype)
         _cuda_contig(token_ids, "token ids", torch.int32)
-        _need(out_dtype in _DT and u.dim() == 2 and table.dim() == 2 and table.shape[1] == u.shape[1] and token_ids.numel() == u.shape[0],
-              "side_gate: u [T, s], table [vocab, s], one token per row")
-        out = torch.empty(u.shape, dtype=out_dtype, device=u.device)
-        rc = self._lib("stream_sum").tl_side_gate(_ptr(u), _ptr(token_ids), _ptr(table), _ptr(out), _DT[out_dtype], u.shape[0], u.shape[1],
+        splits = u.shape[0] if u.dim() == 3 else 1
+        _need(out_dtype in _DT and u.dim() in (2, 3) and table.dim() == 2 and table.shape[1] == u.shape[-1]
+              and token_ids.numel() == u.shape[-2], "side_gate: u [T, s], table [vocab, s], one token per row")
+        _need(u.dtype == torch.float32 or (u.dtype == out_dtype and splits == 1), "side_gate: u of the output's dtype, or float32")
+        out = torch.empty(u.shape[-2:], dtype=out_dtype, device=u.device)
+        rc = self._lib("stream_sum").tl_side_gate(_ptr(u), _DT[u.dtype], splits, ctypes.c_longlong(u.stride(0) if splits > 1 else 0),
+                                                 _ptr(token_ids), _ptr(table), _ptr(out), _DT[out_dtype], u.shape[-2], u.shape[-1],
                                                  table.shape[0], _stream())
         _check(rc, "side_gate")
         self.launches += 1
@@ -1102,7 +1130,7 @@ class NativeOps:
             parts = self.gemm_tcgen05(x, w, out_dtype)
             if parts.dim() == 2 or partials_ok:
                 return parts
-            return parts.sum(0).to(out_dtype)
+            return self.sum_partials(parts, out_dtype)
         if out_dtype == torch.bfloat16:
             return torch.mm(x, w.t())
         _need(out_dtype == torch.float32, f"linear: output dtype {out_dtype} unsupported")

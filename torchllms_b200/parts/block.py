@@ -318,14 +318,14 @@ class ParallelBlock(Block):
             if isinstance(term, NormedSum):
                 normed, coef, eps = term.terms, term.coef, term.eps
             elif isinstance(term, PendingProduct):
-                plain.append(term.take(ops, partials_ok=False))
+                plain.append(term.take(ops, partials_ok=True))
             elif term is not None:
                 plain.append(term)
         rows = ops.stream_add(residual.h, normed=normed, coef=coef, eps=eps, plain=tuple(plain), out_dtype=self.env.dtype)
         residual.rows = rows
         if not self.side_dim:
             return
-        u = ops.linear(rows, self.side_gate_w)
+        u = ops.linear(rows, self.side_gate_w, partials_ok=True)
         g = ops.side_gate(u, ctx.token_ids, self.side_table, out_dtype=self.env.dtype)
         follow = residual.next_norm
         if isinstance(follow, RMSNorm):

@@ -146,5 +146,5 @@ class PolyNormFeedForward(FeedForward):
 
     def forward(self, x: torch.Tensor, ctx) -> PendingProduct:
         ops = self.env.ops
-        y = ops.polynorm(ops.linear(x, self.w_up), self.coef, self.eps, out_dtype=self.env.dtype)
+        y = ops.polynorm(ops.linear(x, self.w_up, partials_ok=True), self.coef, self.eps, out_dtype=self.env.dtype)
         return PendingProduct(y, self.w_down)

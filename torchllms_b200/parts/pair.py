@@ -70,6 +70,6 @@ class SideBySide(Mixer):
             state = None if m.state_need() is None else state_field(cache.state, self._need, prefix)
             y = m.forward(x, ctx, dataclasses.replace(cache, state=state))
             if isinstance(y, PendingProduct):
-                y = y.take(self.env.ops, partials_ok=False)
+                y = y.take(self.env.ops, partials_ok=True)
             terms.append((y, self.out_w[prefix]))
         return NormedSum(tuple(terms), self.coef, self.eps)
