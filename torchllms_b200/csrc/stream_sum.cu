@@ -149,7 +149,15 @@ __global__ void sum_partials_kernel(const float* __restrict__ parts, int splits,
     }
 }
 
-int row_threads(int width) { return width >= 2048 ? 512 : width >= 512 ? 256 : 128; }
+// threads of a CTA that owns a row: few rows (a decode step, whose terms are often many planes of partial sums) are
+// all the parallelism there is, so a row gets as many threads as it has pairs of columns
+int row_threads(int width, int n_rows) {
+    if (n_rows <= 64) {
+        const int t = ((width / 2 + 31) / 32) * 32;
+        return t > 1024 ? 1024 : t < 128 ? 128 : t;
+    }
+    return width >= 2048 ? 512 : width >= 512 ? 256 : 128;
+}
 
 }  // namespace
 
@@ -176,7 +184,7 @@ extern "C" int tl_stream_add(float* h, const void* const* normed, const int* nor
         if (plain_splits[i] < 1 || (plain_splits[i] > 1 && plain_dtype[i] != TL_F32)) return TL_BAD_SIZE;
         p.plain[i] = plain[i]; p.plain_dtype[i] = plain_dtype[i]; p.plain_splits[i] = plain_splits[i]; p.plain_plane[i] = plain_plane[i];
     }
-    return (int)tl_launch(stream_add_kernel, dim3(n_tokens), dim3(row_threads(dim)), 0, (cudaStream_t)stream, p);
+    return (int)tl_launch(stream_add_kernel, dim3(n_tokens), dim3(row_threads(dim, n_tokens)), 0, (cudaStream_t)stream, p);
 }
 
 // z: [splits][n_tokens][width]; coef: float32 [4] = (a, b, c, e); out: [n_tokens][width].
@@ -184,7 +192,7 @@ extern "C" int tl_polynorm(const void* z, int in_dtype, int splits, long long pl
                            int n_tokens, int width, float eps, void* stream) {
     if (n_tokens <= 0) return TL_OK;
     if (width <= 0 || splits < 1 || (splits > 1 && in_dtype != TL_F32)) return TL_BAD_SIZE;
-    const dim3 grid(n_tokens), block(row_threads(width));
+    const dim3 grid(n_tokens), block(row_threads(width, n_tokens));
     cudaStream_t s = (cudaStream_t)stream;
     if (in_dtype == TL_F32 && out_dtype == TL_F32)
         return (int)tl_launch(polynorm_kernel<float, float>, grid, block, 0, s, (const float*)z, splits, plane, coef, (float*)out, width, eps);
