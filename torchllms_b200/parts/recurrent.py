@@ -82,7 +82,8 @@ class Retention(Mixer):
     ``"half"``: coordinate ``i`` with ``i + rot_dims / 2``), k then multiplied by ``k_scale``.  Each
     head's ``o`` is divided by its root mean square (no weight), multiplied by ``silu(wg x)`` and
     projected by ``wo``.  Rotation, recurrence, state and the head norm are float32; one stacked
-    product gives ``[q | k | v | g]``."""
+    product gives ``[q | k | v | g]``.  The state rows hold ``S^T`` (``[heads, v_head_dim, head_dim]``:
+    a column's keys side by side, as the kernel's lanes read them)."""
 
     graph_safe = True
 
@@ -146,8 +147,8 @@ class GatedDelta(Mixer):
     multiplied by ``q_scale``.  Each head's ``o`` is RMS-normed over its values with the weight
     ``norm.weight`` (shared by heads), multiplied by ``silu(wg x)`` and projected by ``wo``.
 
-    State per request: the convolutions' last ``conv_taps - 1`` inputs and the heads' matrices, all
-    float32.  One stacked product gives ``[q | k | v | b | a | g]``."""
+    State per request: the convolutions' last ``conv_taps - 1`` inputs and the heads' matrices (kept
+    as ``S^T``, ``[heads, v_head_dim, head_dim]``), all float32.  One stacked product gives ``[q | k | v | b | a | g]``."""
 
     graph_safe = True
 
