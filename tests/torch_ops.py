@@ -66,12 +66,23 @@ class TorchOps:
     def stream_rows(self, h, dtype):
         return h if dtype == torch.float32 else h.to(dtype)
 
+    def stream_inject(self, h, rows, row):
+        """h += rows (float32 [T, dim] or None) + row (float32 [dim] or None), in place."""
+        if rows is not None:
+            h += rows
+        if row is not None:
+            h += row
+
     def norm_add(self, h, delta, weight, eps, out_dtype, then_weight=None, then_eps=0.0):
         """h += delta / sqrt(mean(delta^2) + eps) * weight (in place, float32); the new rows in out_dtype,
         or, with then_weight, their RMS norm under that weight."""
+        bias = None
         if isinstance(delta, PendingProduct):
-            delta = delta.take(self)
+            bias = delta.bias
+            delta = self.linear(delta.x, delta.w, partials_ok=True)
         d = delta.float().sum(0) if delta.dim() == 3 else delta.float()
+        if bias is not None:
+            d = d + bias
         h += d * torch.rsqrt(d.pow(2).mean(-1, keepdim=True) + eps) * weight
         if then_weight is not None:
             return (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + then_eps) * then_weight).to(out_dtype)
@@ -111,11 +122,13 @@ class TorchOps:
         return self.gated_act(self.linear(x, w_gate_up, partials_ok=True), activation, out_dtype=x.dtype)
 
     def rope_store(self, proj, positions, table, *, n_q_heads, n_k_heads, n_v_heads, head_dim, v_head_dim, rot_dims,
-                   interleaved, n_extra, k_pages, v_pages, slot_mapping, page_size, out_dtype):
+                   interleaved, n_extra, k_pages, v_pages, slot_mapping, page_size, out_dtype, bias=None):
         """A row of proj is [q heads | k heads | v heads | extra]: the first rot_dims coordinates of every q
         and k head rotated by the position's angles, k and v written to their pages, sigmoid of the extra
         columns."""
         x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
+        if bias is not None:
+            x = x + bias
         T = x.shape[0]
         nq, nk, nv = n_q_heads * head_dim, n_k_heads * head_dim, n_v_heads * v_head_dim
         assert x.shape[1] == nq + nk + nv + n_extra
@@ -171,20 +184,34 @@ class TorchOps:
             state[slot] = s
         return out.to(out_dtype)
 
-    def moe_route(self, x, w_router, correction, *, n_experts, top, scale, renormalize, shared_gate, logit_bias=None):
+    def moe_route(self, x, w_router, correction, *, n_experts, top, scale, renormalize, shared_gate, logit_bias=None,
+                  score="softmax", n_groups=1, keep_groups=1, group_score_top=2, renorm_eps=0.0):
         z = x.float() @ w_router.t()
         if logit_bias is not None:
             z[:, :n_experts] += logit_bias
-        s = torch.softmax(z[:, :n_experts], dim=-1)
+        s = torch.softmax(z[:, :n_experts], dim=-1) if score == "softmax" else torch.sigmoid(z[:, :n_experts])
         choice = s if correction is None else s + correction
+        if n_groups > 1:
+            per = n_experts // n_groups
+            g = choice.view(-1, n_groups, per).topk(min(group_score_top, per), dim=-1).values.sum(-1)
+            kept = torch.zeros_like(g, dtype=torch.bool).scatter_(1, g.topk(keep_groups, dim=-1).indices, True)
+            choice = choice.masked_fill(~kept[:, :, None].expand(-1, -1, per).reshape(choice.shape), float("-inf"))
         chosen = torch.topk(choice, top, dim=-1).indices
         w = torch.gather(s, 1, chosen)
         if renormalize:
-            w = w / w.sum(-1, keepdim=True)
+            w = w / (w.sum(-1, keepdim=True) + np.float32(renorm_eps))
         gate = torch.sigmoid(z[:, n_experts]).contiguous() if shared_gate else None
         return chosen.to(torch.int32).contiguous(), (w * np.float32(scale)).contiguous(), gate
 
-    def moe_experts(self, x, chosen, weights, w_up, w_down, *, activation, shared=None, shared_gate=None, gated=False):
+    def _gated(self, gate, up, activation, act_params):
+        if activation == "clamped_swish":
+            limit, alpha, offset = act_params
+            g = gate.clamp(max=limit)
+            return g * torch.sigmoid(alpha * g) * (up.clamp(min=-limit, max=limit) + offset)
+        return self._act(gate, activation) * up
+
+    def moe_experts(self, x, chosen, weights, w_up, w_down, *, activation, shared=None, shared_gate=None, gated=False,
+                    act_params=None):
         """w_up [E, hidden, dim] (gated: [E, 2 * hidden, dim], rows [gate; up]); w_down [dim, >= E * hidden], expert e's
         matrix in columns e * hidden ..."""
         T, top = chosen.shape
@@ -195,7 +222,7 @@ class TorchOps:
                 rows = (chosen[:, k] == e).nonzero().flatten()
                 u = x[rows].float() @ w_up[e].float().t()
                 if gated:
-                    u = (self._act(u[:, :hidden].to(x.dtype).float(), activation) * u[:, hidden:].to(x.dtype).float()).to(x.dtype)
+                    u = self._gated(u[:, :hidden].to(x.dtype).float(), u[:, hidden:].to(x.dtype).float(), activation, act_params).to(x.dtype)
                 else:
                     u = self._act(u, activation).to(x.dtype)
                 y = (u.float() @ w_down[:, e * hidden:(e + 1) * hidden].float().t()).to(x.dtype)
@@ -210,12 +237,17 @@ class TorchOps:
     def moe_prefers_dense(self, n_tokens, top, n_experts, dtype):
         return self.dense_experts
 
-    def moe_dense_hidden(self, x, chosen, weights, gate, w_up_all, *, n_experts, hidden, activation, gated=False):
+    def moe_dense_hidden(self, x, chosen, weights, gate, w_up_all, *, n_experts, hidden, activation, gated=False,
+                         act_params=None, extra_act_params=None):
         T = x.shape[0]
         u = x.float() @ w_up_all.float().t()
-        if gated:            # an expert's columns are [gate | up]
-            u = u.view(T, n_experts, 2, hidden)
-            u = (self._act(u[:, :, 0], activation) * u[:, :, 1]).reshape(T, n_experts * hidden)
+        if gated:            # an expert's columns are [gate | up]; what follows the experts is a shared expert's [gate | up]
+            rest = u[:, n_experts * 2 * hidden:]
+            u = u[:, :n_experts * 2 * hidden].view(T, n_experts, 2, hidden)
+            u = self._gated(u[:, :, 0], u[:, :, 1], activation, act_params).reshape(T, n_experts * hidden)
+            if rest.shape[1]:
+                sh = rest.shape[1] // 2
+                u = torch.cat([u, self._gated(rest[:, :sh], rest[:, sh:], activation, extra_act_params or act_params)], dim=1)
         else:
             u = self._act(u, activation)
         scale = torch.zeros((T, n_experts), dtype=torch.float32, device=x.device)
@@ -277,7 +309,8 @@ class TorchOps:
             h += p.float().sum(0) if p.dim() == 3 else p.float()
         return self.stream_rows(h, out_dtype)
 
-    def short_conv(self, x, w, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, activation, residual, out_dtype):
+    def short_conv(self, x, w, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, activation, residual, out_dtype,
+                   bias=None):
         """Causal convolution over time per channel: out_t = sum_j w[:, j] x_(t - taps + 1 + j) (+ x_t with residual),
         then the activation.  state [slots, taps - 1, C] holds every request's last inputs (zeros for a fresh one)."""
         C, taps = w.shape
@@ -295,6 +328,8 @@ class TorchOps:
                 full = rows
             y = sum(full[j:j + rows.shape[0]] * w[:, j] for j in range(taps))
             out[qs[b]:qs[b + 1]] = y + rows if residual else y
+        if bias is not None:
+            out = out + bias
         if activation is not None:
             out = self._act(out, activation)
         return out.to(out_dtype)
@@ -366,9 +401,64 @@ class TorchOps:
         n = lambda y: y * torch.rsqrt(y.pow(2).mean(-1, keepdim=True) + eps)
         return (coef[0] * n(z) + coef[1] * n(z * z) + coef[2] * n(z * z * z) + coef[3]).to(out_dtype)
 
-    def head_linear(self, x, w):
-        """x [T, H, K] against w [H, N, K]: out[t, h] = w[h] @ x[t, h]."""
-        return torch.einsum("thk,hnk->thn", x.float(), w.float()).to(x.dtype).contiguous()
+    def head_linear(self, x, w, gate=None):
+        """x [T, H, K] against w [H, N, K]: out[t, h] = w[h] @ x[t, h] (times gate [T, H * N] where given)."""
+        out = torch.einsum("thk,hnk->thn", x.float(), w.float()).to(x.dtype)
+        if gate is not None:
+            out = (out.float() * gate.float().view(out.shape)).to(x.dtype)
+        return out.contiguous()
+
+    def latent_store(self, proj, positions, table, *, n_q, n_latent, n_rot, n_extra, q_norm, latent_norm, eps, interleaved,
+                     k_pages, slot_mapping, page_size, out_dtype):
+        """A row of proj is [q latent | kv latent | rotated key part | extra]: both latents RMS-normed under their
+        weights, the key part rotated by the position, [kv latent | key part] written to the pages, the q latent and
+        sigmoid(extra) returned."""
+        x = proj.float().sum(0) if proj.dim() == 3 else proj.float()
+        assert x.shape[1] == n_q + n_latent + n_rot + n_extra
+        q, c, r, e = x.split([n_q, n_latent, n_rot, n_extra], dim=1)
+        q = q * torch.rsqrt(q.pow(2).mean(-1, keepdim=True) + eps) * q_norm
+        c = c * torch.rsqrt(c.pow(2).mean(-1, keepdim=True) + eps) * latent_norm
+        r = self._turn(r[:, None, :], positions, table, n_rot, interleaved)[:, 0]
+        sm = slot_mapping.long()
+        k_pages[sm // page_size, 0, sm % page_size] = torch.cat([c, r], dim=1).to(k_pages.dtype)
+        return q.to(out_dtype).contiguous(), (torch.sigmoid(e).to(out_dtype).contiguous() if n_extra else None)
+
+    @staticmethod
+    def _turn(y, positions, table, rot, interleaved):
+        """y [T, heads, >= rot] float32: its first rot coordinates rotated by the positions' angles."""
+        y = y.clone()
+        if rot:
+            cs = table[positions.long()][:, None, :rot // 2]
+            r = y[..., :rot]
+            a, b = (r[..., 0::2], r[..., 1::2]) if interleaved else (r[..., :rot // 2], r[..., rot // 2:])
+            ya, yb = a * cs[..., 0] - b * cs[..., 1], b * cs[..., 0] + a * cs[..., 1]
+            if interleaved:
+                y[..., 0:rot:2], y[..., 1:rot:2] = ya, yb
+            else:
+                y[..., :rot // 2], y[..., rot // 2:rot] = ya, yb
+        return y
+
+    def latent_query(self, q, w_uk_t, positions, table, *, rot_dim, interleaved):
+        """q [T, H, d + rot_dim], w_uk_t [H, rank, d]: [w_uk_t[h] @ q[t, h, :d] | rotated q[t, h, d:]]."""
+        d = q.shape[2] - rot_dim
+        lat = torch.einsum("thk,hnk->thn", q[..., :d].float(), w_uk_t.float())
+        rot = self._turn(q[..., d:].float(), positions, table, rot_dim, interleaved)
+        return torch.cat([lat, rot], dim=-1).to(q.dtype).contiguous()
+
+    def selective_scan(self, x, dt, B, C, z, A, D, dt_bias, state, q_start, state_slot, fresh, *, n_seqs, max_q_len, out_dtype):
+        """S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n with dt = softplus(dt + dt_bias); y = S C + D x; out = y silu(z)."""
+        xf, zf, Bf, Cf = x.float(), z.float(), B.float(), C.float()
+        step = torch.nn.functional.softplus(dt.float() + dt_bias)
+        out = torch.empty(xf.shape, dtype=torch.float32, device=x.device)
+        qs = q_start.tolist()
+        for b in range(n_seqs):
+            slot = int(state_slot[b])
+            S = torch.zeros_like(state[slot]) if int(fresh[b]) else state[slot].clone()
+            for t in range(qs[b], qs[b + 1]):
+                S = torch.exp(step[t][:, None] * A) * S + (step[t] * xf[t])[:, None] * Bf[t][None, :]
+                out[t] = (S @ Cf[t] + D * xf[t]) * (zf[t] * torch.sigmoid(zf[t]))
+            state[slot] = S
+        return out.to(out_dtype)
 
     def rmsnorm(self, h, delta, weight, eps, out_dtype, rows=None, deferred=False):
         if isinstance(delta, PendingProduct):
@@ -469,15 +559,16 @@ class TorchOps:
     def paged_attention(self, q, k_pages, v_pages, block_table, q_start, kv_len, *, n_seqs, max_q_len,
                         max_kv_len, scale, window, page_size, allow_split=True, impl="auto", n_tokens=None, out=None,
                         keep_first=0, distance_bias=None, distance_buckets=None, gate=None, n_v_heads=None,
-                        out_dtype=None):
+                        out_dtype=None, softcap=0.0, sinks=None, value_dim=None):
         T, H, hd = q.shape
         KV = k_pages.shape[1]
         group = H // KV
         if keep_first or distance_bias is not None or gate is not None or v_pages.shape[3] != hd \
-                or v_pages.shape[1] != KV or out_dtype not in (None, q.dtype):
+                or v_pages.shape[1] != KV or out_dtype not in (None, q.dtype) or softcap or sinks is not None or value_dim:
             assert out is None and n_tokens is None and (n_v_heads or KV) == v_pages.shape[1]
             return self._attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window,
-                                           page_size, keep_first, distance_bias, distance_buckets, gate, out_dtype)
+                                           page_size, keep_first, distance_bias, distance_buckets, gate, out_dtype,
+                                           softcap, sinks, value_dim)
         # the same contract as the kernels' front end: the step's bounds cover its requests and fit the table
         assert block_table.shape[1] * page_size >= max_kv_len, "block_table is too narrow for max_kv_len"
         assert int(kv_len[:n_seqs].max()) <= max_kv_len and n_seqs <= block_table.shape[0]
@@ -506,12 +597,15 @@ class TorchOps:
         return out
 
     def _attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, scale, window, page_size,
-                           keep_first, distance_bias, distance_buckets, gate, out_dtype=None):
+                           keep_first, distance_bias, distance_buckets, gate, out_dtype=None, softcap=0.0, sinks=None,
+                           value_dim=None):
         """Everything the general kernel can do, key by visible key: kept first tokens behind a
         window, a bias by bucketed distance, values of another size, an output gate per head
         ([T, H]) or per element ([T, H * dv])."""
         T, H, hd = q.shape
         KV, dv, VH = k_pages.shape[1], v_pages.shape[3], v_pages.shape[1]
+        if value_dim:        # a stored value is the first so many coordinates of a stored vector
+            dv = int(value_dim)
         group = H // KV
         out = torch.zeros((T, H, dv), dtype=out_dtype or q.dtype, device=q.device)
         qs, kl = q_start.tolist(), kv_len.tolist()
@@ -523,7 +617,7 @@ class TorchOps:
             pages = block_table[b].long()[pos // page_size]
             assert (pages >= 0).all(), "attention would read a page that was given back"
             k = k_pages[pages, :, pos % page_size].float()
-            v = v_pages[pages, :, pos % page_size].float()
+            v = v_pages[pages, :, pos % page_size].float()[..., :dv]
             qq = q[qs[b]:qs[b + 1]].float()
             dist = qpos[:, None] - pos[None, :]
             hidden = dist < 0
@@ -533,7 +627,14 @@ class TorchOps:
                 s = (qq[:, h] @ k[:, h // group].T) * scale
                 if distance_bias is not None:
                     s = s + distance_bias[distance_buckets[dist.clamp(min=0)].long(), h]
-                o = torch.softmax(s.masked_fill(hidden, float("-inf")), -1) @ v[:, (h // group) % VH]
+                if softcap:
+                    s = np.float32(softcap) * torch.tanh(s / np.float32(softcap))
+                s = s.masked_fill(hidden, float("-inf"))
+                if sinks is not None:        # one more term in the denominator, without a value
+                    s = torch.cat([s, sinks[h].expand(ql, 1)], dim=1)
+                    o = torch.softmax(s, -1)[:, :-1] @ v[:, (h // group) % VH]
+                else:
+                    o = torch.softmax(s, -1) @ v[:, (h // group) % VH]
                 if gate is not None:
                     g = gate[qs[b]:qs[b + 1]].float()
                     o = o * (g[:, h:h + 1] if gate.shape[1] == H else g.view(ql, H, dv)[:, h])

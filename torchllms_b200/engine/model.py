@@ -41,6 +41,8 @@ class Model:
         self.embedding: Optional[torch.Tensor] = None
         self.position_table: Optional[torch.Tensor] = None
         self.head: Optional[torch.Tensor] = None
+        self.row_tensors: Dict[str, torch.Tensor] = {}
+        self.keeps_embedding = any(run.add_embedding for run in spec.run_order)
 
     # ----------------------------------------------------------------- weights
     def expected_tensors(self) -> Dict[str, ExpectedTensor]:
@@ -58,6 +60,8 @@ class Model:
                 out[f"{spec.embedding_norm_prefix}.{name}"] = e
         if not spec.tie_head:
             out[spec.head_tensor] = ExpectedTensor((spec.vocab_size, spec.dim))
+        for name, rows in spec.row_tensors:
+            out[name] = ExpectedTensor((rows, spec.dim))
         return out
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
@@ -74,6 +78,9 @@ class Model:
             self.embedding_norm.load({name: tensors[f"{spec.embedding_norm_prefix}.{name}"]
                                       for name in self.embedding_norm.expected_tensors()})
         self.head = self.embedding if spec.tie_head else as_compute(tensors[spec.head_tensor], self.env)
+        # rows that runs add to the stream: kept in 32-bit, as the stream is
+        self.row_tensors = {name: tensors[name].to(device=self.device, dtype=torch.float32).contiguous()
+                            for name, _rows in spec.row_tensors}
 
     def weight_bytes(self) -> int:
         """Bytes of weights a step has to read: every layer's matrices and the head once
@@ -109,6 +116,16 @@ class Model:
         nxt.copy_(residual.h)
         residual.h, residual.rows = nxt, None
 
+    def _add_before_run(self, residual: Residual, run, embedding_output: Optional[torch.Tensor]) -> None:
+        """``h += embedding output + row`` (either may be absent), in 32-bit, before a run that asks for it."""
+        if residual.delta is not None or residual.normed is not None or residual.history is not None:
+            raise RuntimeError("a sum in front of a run needs a stream with nothing pending and no kept history")
+        row = None
+        if run.add_row is not None:
+            row = self.row_tensors[run.add_row[0]][run.add_row[1]]
+        self.ops.stream_inject(residual.h, embedding_output if run.add_embedding else None, row)
+        residual.rows = None
+
     def forward(self, ctx, views: Sequence) -> Optional[torch.Tensor]:
         """Run the step's tokens; returns float32 logits ``[n_wanted, vocab]`` or ``None``."""
         first = self.blocks[self.spec.run_order[0].layer] if self.spec.run_order else None
@@ -131,8 +148,14 @@ class Model:
             residual = Residual(self.ops.rmsnorm(residual.h, None, self.embedding_norm.weight, self.embedding_norm.eps,
                                                  out_dtype=torch.float32))
         order = self.spec.run_order
+        embedding_output = residual.h.clone() if self.keeps_embedding else None
         for i, run in enumerate(order):
-            residual.next_norm = self.blocks[order[i + 1].layer].input_norm if i + 1 < len(order) else None
+            if run.add_embedding or run.add_row is not None:
+                self._add_before_run(residual, run, embedding_output)
+            follows = order[i + 1] if i + 1 < len(order) else None
+            # (a run that starts with a sum onto the stream takes its own input norm afterwards)
+            residual.next_norm = (self.blocks[follows.layer].input_norm
+                                  if follows is not None and not (follows.add_embedding or follows.add_row is not None) else None)
             self.blocks[run.layer].forward(residual, ctx, views[i])
             if residual.history is not None and residual.level != i + 1:
                 self._next_level(residual)      # a block that reads no earlier results: the stream passes as it is

@@ -29,6 +29,7 @@ produces ``x`` finish without a pass over the whole row.
 from __future__ import annotations
 
 from dataclasses import dataclass
+from typing import Optional
 
 import torch
 
@@ -37,9 +38,12 @@ import torch
 class PendingProduct:
     x: torch.Tensor          # [T, K], activation dtype
     w: torch.Tensor          # [N, K], the weight as nn.Linear keeps it
+    bias: Optional[torch.Tensor] = None      # float32 [N], added by whoever adds the product up (the norm kernels on a sublayer's output take it)
 
     def take(self, ops, partials_ok: bool = True):
         """The product as a tensor (or float32 partial sums when ``partials_ok``)."""
+        if self.bias is not None:
+            raise RuntimeError("a pending product with a bias is taken by a kernel that adds the bias (norm_add)")
         return ops.linear(self.x, self.w, partials_ok=partials_ok)
 
     @property

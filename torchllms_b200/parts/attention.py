@@ -330,3 +330,104 @@ class DifferentialAttention(Mixer):
         o = ops.differential_combine(maps, self.lam, eps=self.norm_eps, out_scale=1.0 - self.lambda_init, gate=gate,
                                      out_dtype=self.env.dtype)
         return PendingProduct(o, self.wo)
+
+
+@register_mixer("rotary_gated_attention")
+class RotaryGatedAttention(Mixer):
+    """Grouped-query attention with rotary positions and the options below, all of them numbers or
+    switches of the spec:
+
+    * projections ``wq, wk, wv`` (and ``wo``) with optional biases (``qkv_bias``, ``out_bias``), keys and
+      values of sizes of their own (``head_dim``, ``v_head_dim``);
+    * rotation of the first ``rot_dims`` coordinates of every q and k head by ``p * rot_base^(-2i/rot_dims)``
+      (``rot_pairing`` ``"interleaved"``: coordinate ``2i`` with ``2i + 1``; ``"half"``: ``i`` with ``i + rot_dims / 2``);
+    * score ``= q . k * scale``, then, with ``softcap = c > 0``, ``c * tanh(score / c)``;
+    * causal, optionally behind a sliding ``window``;
+    * softmax whose denominator, with ``sinks``, also holds ``exp(sinks[h])``: a learned number per head
+      (tensor ``sinks``) that stands for a key without a value and is neither scaled nor capped;
+    * an output gate ``sigmoid(wg x)``, one number per head (``gate="head"``) or per element
+      (``"element"``), ahead of ``wo``.
+
+    One stacked product gives q, k, v and the gate's logits; one kernel adds the biases, rotates,
+    stores keys and values and takes the gate's sigmoid; cap, sink and gate live in the attention
+    kernel; the output bias is added where the output product is added up."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, n_heads: int, n_kv_heads: int, head_dim: int,
+                 v_head_dim: Optional[int] = None, scale: float, softcap: float = 0.0, sinks: bool = False,
+                 rot_dims: int = 0, rot_base: float = 10000.0, rot_pairing: str = "interleaved", window: Optional[int] = None,
+                 qkv_bias: bool = False, out_bias: bool = False, gate: Optional[str] = None):
+        if n_heads % n_kv_heads != 0:
+            raise ValueError(f"n_heads ({n_heads}) must be a multiple of n_kv_heads ({n_kv_heads})")
+        if rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim:
+            raise ValueError(f"rot_dims must be even and at most head_dim ({head_dim}), got {rot_dims}")
+        if rot_pairing not in ("half", "interleaved"):
+            raise ValueError(f"rot_pairing must be 'half' or 'interleaved', got {rot_pairing!r}")
+        if gate not in (None, "element", "head"):
+            raise ValueError(f"gate must be None, 'element' or 'head', got {gate!r}")
+        if softcap < 0:
+            raise ValueError(f"softcap must not be negative, got {softcap}")
+        self.env = env
+        self.dim, self.n_heads, self.n_kv_heads = int(dim), int(n_heads), int(n_kv_heads)
+        self.head_dim = int(head_dim)
+        self.v_head_dim = int(v_head_dim if v_head_dim is not None else head_dim)
+        self.scale, self.softcap = float(scale), float(softcap)
+        self.has_sinks, self.qkv_bias, self.out_bias, self.gate = bool(sinks), bool(qkv_bias), bool(out_bias), gate
+        self.rot_dims, self.interleaved = int(rot_dims), rot_pairing == "interleaved"
+        self.window = None if window is None else int(window)
+        self.n_q, self.n_k, self.n_v = self.n_heads * self.head_dim, self.n_kv_heads * self.head_dim, self.n_kv_heads * self.v_head_dim
+        self.n_g = {None: 0, "head": self.n_heads, "element": self.n_heads * self.v_head_dim}[gate]
+        env.ops.check_attention_sizes(self.n_heads, self.n_kv_heads, self.head_dim, env.dtype, v_head_dim=self.v_head_dim)
+        self.table = precise_rotary_table(max(self.rot_dims, 2), rot_base, 1.0, env.max_positions, env.device)
+        self.w_in = self.b_in = self.sinks = self.wo = self.bo = None
+
+    def cache_need(self) -> CacheNeed:
+        if self.window is None:
+            return CacheNeed("full", self.n_kv_heads, self.head_dim, None, self.v_head_dim)
+        return CacheNeed("window", self.n_kv_heads, self.head_dim, self.window, self.v_head_dim)
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        out = {"wq.weight": ExpectedTensor((self.n_q, self.dim)), "wk.weight": ExpectedTensor((self.n_k, self.dim)),
+               "wv.weight": ExpectedTensor((self.n_v, self.dim)),
+               "wo.weight": ExpectedTensor((self.dim, self.n_heads * self.v_head_dim))}
+        if self.qkv_bias:
+            out.update({"wq.bias": ExpectedTensor((self.n_q,)), "wk.bias": ExpectedTensor((self.n_k,)),
+                        "wv.bias": ExpectedTensor((self.n_v,))})
+        if self.out_bias:
+            out["wo.bias"] = ExpectedTensor((self.dim,))
+        if self.has_sinks:
+            out["sinks"] = ExpectedTensor((self.n_heads,))
+        if self.gate:
+            out["wg.weight"] = ExpectedTensor((self.n_g, self.dim))
+        return out
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f32 = dict(device=self.env.device, dtype=torch.float32)
+        names = ["wq.weight", "wk.weight", "wv.weight"] + (["wg.weight"] if self.gate else [])
+        self.w_in = torch.cat([as_compute(tensors[n], self.env) for n in names])       # rows [wq; wk; wv; wg]
+        if self.qkv_bias:
+            self.b_in = torch.cat([tensors[n].to(**f32) for n in ("wq.bias", "wk.bias", "wv.bias")]
+                                  + [torch.zeros(self.n_g, **f32)]).contiguous()
+        if self.out_bias:
+            self.bo = tensors["wo.bias"].to(**f32).contiguous()
+        if self.has_sinks:
+            self.sinks = tensors["sinks"].to(**f32).contiguous()
+        self.wo = as_compute(tensors["wo.weight"], self.env)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.wo))
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> PendingProduct:
+        ops = self.env.ops
+        proj = ops.linear(x, self.w_in, partials_ok=True)
+        q, gate = ops.rope_store(
+            proj, ctx.positions, self.table, n_q_heads=self.n_heads, n_k_heads=self.n_kv_heads, n_v_heads=self.n_kv_heads,
+            head_dim=self.head_dim, v_head_dim=self.v_head_dim, rot_dims=self.rot_dims, interleaved=self.interleaved,
+            n_extra=self.n_g, k_pages=cache.k_pages, v_pages=cache.v_pages, slot_mapping=cache.slot_mapping,
+            page_size=cache.page_size, out_dtype=self.env.dtype, bias=self.b_in)
+        o = ops.paged_attention(
+            q, cache.k_pages, cache.v_pages, cache.block_table, ctx.q_start, ctx.kv_len, n_seqs=ctx.n_seqs,
+            max_q_len=ctx.max_q_len, max_kv_len=ctx.max_kv_len, scale=self.scale, window=self.window,
+            page_size=cache.page_size, gate=gate, softcap=self.softcap, sinks=self.sinks, impl="auto")
+        return PendingProduct(o.view(o.shape[0], self.n_heads * self.v_head_dim), self.wo, bias=self.bo)

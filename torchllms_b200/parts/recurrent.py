@@ -212,3 +212,73 @@ class GatedDelta(Mixer):
                                decay_rate=self.decay_rate, decay_bias=self.decay_bias)
         y = ops.head_norm_gate(o, proj[:, nc + 2 * H:], self.norm_w, self.norm_eps, head_dim=self.v_head_dim, out_dtype=self.env.dtype)
         return PendingProduct(y, self.wo)
+
+
+@register_mixer("selective_scan")
+class SelectiveScan(Mixer):
+    """A selective state-space mixer: every channel keeps ``state`` numbers that decay and are fed
+    at rates the token itself chooses.
+
+        ``[x | z] = W_in h``;  ``x <- silu(conv(x) + conv_bias)`` (causal, ``conv_taps`` taps per channel);
+        ``[r | B | C] = W_x x`` (``dt_rank``, ``state``, ``state`` numbers);  ``dt = softplus(W_dt r + dt_bias)``;
+        ``S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n``,  ``A = -exp(A_log)``;
+        ``y_c = sum_n S[c, n] C_n + D_c x_c``;  output ``W_o (y * silu(z))``.
+
+    State per request: the convolution's last ``conv_taps - 1`` inputs and ``S`` (``[inner, state]``),
+    float32.  The step sizes with their softplus, the decays with their exponentials, ``S`` and
+    everything multiplied into it are float32 inside one kernel that walks a request's tokens in
+    order, so a result does not depend on how a prompt was cut.  ``W_dt`` is stored padded with zero
+    columns to the width of ``W_x``'s rows, so that it multiplies those rows as they lie."""
+
+    graph_safe = True
+
+    def __init__(self, env: BuildEnv, *, dim: int, inner: int, state: int, dt_rank: int, conv_taps: int):
+        if min(inner, state, dt_rank, conv_taps) < 1:
+            raise ValueError("the sizes of a selective scan must be positive")
+        self.env = env
+        self.dim, self.inner, self.state, self.dt_rank, self.taps = int(dim), int(inner), int(state), int(dt_rank), int(conv_taps)
+        self.n_x = self.dt_rank + 2 * self.state
+        self._need = join_states([("conv", StateNeed((self.taps - 1, self.inner)) if self.taps > 1 else None),
+                                  ("scan", StateNeed((self.inner, self.state)))])
+        self.w_in = self.w_conv = self.b_conv = self.w_x = self.w_dt = self.b_dt = self.A = self.D = self.wo = None
+
+    def state_need(self) -> StateNeed:
+        return self._need
+
+    def expected_tensors(self) -> Dict[str, ExpectedTensor]:
+        d, c = self.dim, self.inner
+        return {"w_in.weight": ExpectedTensor((2 * c, d)), "conv.weight": ExpectedTensor((c, self.taps)),
+                "conv.bias": ExpectedTensor((c,)), "w_x.weight": ExpectedTensor((self.n_x, c)),
+                "w_dt.weight": ExpectedTensor((c, self.dt_rank)), "w_dt.bias": ExpectedTensor((c,)),
+                "A_log": ExpectedTensor((c, self.state)), "D": ExpectedTensor((c,)), "wo.weight": ExpectedTensor((d, c))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f32 = dict(device=self.env.device, dtype=torch.float32)
+        self.w_in = as_compute(tensors["w_in.weight"], self.env)
+        self.w_conv = tensors["conv.weight"].to(**f32).contiguous()
+        self.b_conv = tensors["conv.bias"].to(**f32).contiguous()
+        self.w_x = as_compute(tensors["w_x.weight"], self.env)
+        w_dt = torch.zeros((self.inner, self.n_x), dtype=tensors["w_dt.weight"].dtype)
+        w_dt[:, :self.dt_rank] = tensors["w_dt.weight"]
+        self.w_dt = as_compute(w_dt, self.env)
+        self.b_dt = tensors["w_dt.bias"].to(**f32).contiguous()
+        self.A = (-torch.exp(tensors["A_log"].to(**f32))).contiguous()           # taken once
+        self.D = tensors["D"].to(**f32).contiguous()
+        self.wo = as_compute(tensors["wo.weight"], self.env)
+
+    def weight_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.w_in, self.w_x, self.w_dt, self.A, self.wo))
+
+    def forward(self, x: torch.Tensor, ctx, cache) -> PendingProduct:
+        ops = self.env.ops
+        c = self.inner
+        xz = ops.linear(x, self.w_in)
+        conv_state = state_field(cache.state, self._need, "conv") if self.taps > 1 else None
+        u = ops.short_conv(xz[:, :c], self.w_conv, conv_state, ctx.q_start, ctx.state_slot, ctx.fresh, n_seqs=ctx.n_seqs,
+                           max_q_len=ctx.max_q_len, activation="silu", residual=False, out_dtype=self.env.dtype, bias=self.b_conv)
+        p = ops.linear(u, self.w_x)                       # [T, dt_rank + 2 state]
+        dt = ops.linear(p, self.w_dt)                     # [T, inner]: the zero columns skip B and C
+        y = ops.selective_scan(u, dt, p[:, self.dt_rank:self.dt_rank + self.state], p[:, self.dt_rank + self.state:], xz[:, c:],
+                               self.A, self.D, self.b_dt, state_field(cache.state, self._need, "scan"), ctx.q_start,
+                               ctx.state_slot, ctx.fresh, n_seqs=ctx.n_seqs, max_q_len=ctx.max_q_len, out_dtype=self.env.dtype)
+        return PendingProduct(y, self.wo)

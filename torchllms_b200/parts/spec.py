@@ -54,10 +54,17 @@ class LayerSpec:
 @dataclass(frozen=True)
 class RunEntry:
     """One run of a layer.  ``cache_of`` names the run (its index in the run
-    order) whose cache this run reads instead of writing one of its own."""
+    order) whose cache this run reads instead of writing one of its own.
+
+    What may be added to the stream right before the run (a model that runs a span of layers
+    several times starts every pass this way): ``add_embedding`` adds the embedding output (the
+    stream as it was before the first run), ``add_row = (tensor, i)`` adds row ``i`` of a model-level
+    ``[rows, dim]`` tensor (``ModelSpec.row_tensors``) to every token.  Both sums are 32-bit."""
 
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
+    add_row: Optional[Tuple[str, int]] = None
 
 
 @dataclass(frozen=True)
@@ -78,10 +85,14 @@ class ModelSpec:
     embedding_norm: Optional[PartSpec] = None        # a norm applied to the table's row: its result is the stream
     embedding_norm_prefix: str = "embedding_norm"    # prefix of that norm's tensors
     logit_scale: float = 1.0         # the head's products leave multiplied by this
+    row_tensors: Tuple[Tuple[str, int], ...] = ()    # model-level (name, rows) tensors [rows, dim] whose rows runs add to the stream (RunEntry.add_row)
 
     def __post_init__(self):
         n = len(self.layers)
+        rows = dict(self.row_tensors)
         for i, run in enumerate(self.run_order):
+            if run.add_row is not None and not (run.add_row[0] in rows and 0 <= run.add_row[1] < rows[run.add_row[0]]):
+                raise ValueError(f"run {i} adds row {run.add_row[1]} of '{run.add_row[0]}', which the model does not have")
             if not 0 <= run.layer < n:
                 raise ValueError(f"run {i} names layer {run.layer}, but there are {n} layers")
             if run.cache_of is not None:
