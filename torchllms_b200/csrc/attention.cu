@@ -13,6 +13,11 @@
 //                (several attention maps with keys of their own over one set of values)
 //   out_f32      the result is written as float32 whatever q's dtype (for a caller that still
 //                combines maps before anything is rounded)
+//   softcap      c > 0: the scaled score s becomes c * tanh(s / c) (before any bias)
+//   sinks        a learned number per query head, [n_heads] float32: the softmax's denominator also holds
+//                exp(sinks[h]); it stands for a key without a value, counts once, and is neither scaled nor capped
+//   v_stride     elements from one stored value to the next when that is not v_head_dim: with v_pages being
+//                k_pages and v_stride = head_dim, a value is the first v_head_dim coordinates of a stored key
 //
 // What it computes, per query token at absolute position p of request b and query head h
 // (kv head h / (H / KV)):   o = softmax_k( q . k_k * scale ) v_k   over keys k <= p
@@ -53,6 +58,9 @@ struct AttnParams {
     const void* gate;    // [T, n_heads] (gate_mode 1) or [T, n_heads * v_head_dim] (gate_mode 2), in q's dtype
     int gate_mode, n_bucket, keep_first;
     int n_v_heads, out_f32;
+    int v_stride;        // elements between stored values (v_head_dim unless values are parts of wider vectors)
+    float softcap;       // 0: none
+    const float* sinks;  // [n_heads] or null
     int table_stride;
     int n_heads, n_kv_heads, head_dim, v_head_dim, page_size;
     int group, gchunk, n_gchunks, tokens_per_tile;
@@ -130,7 +138,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
     for (int j = 0; j < HD_MAX / 8; ++j) acc[j] = 0.f;
 
     constexpr int VEC = Vec16<T>::N;
-    const bool vec_ok = hd % VEC == 0 && dv % VEC == 0;      // every stored vector starts on 16 bytes
+    const bool vec_ok = hd % VEC == 0 && dv % VEC == 0 && p.v_stride % VEC == 0;      // every stored vector starts on 16 bytes
     const int k_vecs = hd / VEC, v_vecs = dv / VEC;
     const int* table = p.block_table + (size_t)b * p.table_stride;
     const int vh = kvh % p.n_v_heads;        // the value head that goes with this key head
@@ -149,7 +157,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
                     const size_t at = ((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size;
                     const size_t vat = ((size_t)page * p.n_v_heads + vh) * p.page_size + kpos % p.page_size;
                     Vec16<T> x;
-                    x.load(is_k ? k_pages + at * hd + v * VEC : v_pages + vat * dv + (v - k_vecs) * VEC);
+                    x.load(is_k ? k_pages + at * hd + v * VEC : v_pages + vat * p.v_stride + (v - k_vecs) * VEC);
 #pragma unroll
                     for (int e = 0; e < VEC; ++e) dst[e] = x.get(e);
                 } else {
@@ -168,7 +176,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
                     const int page = table[kpos / p.page_size];
                     const size_t at = ((size_t)page * p.n_kv_heads + kvh) * p.page_size + kpos % p.page_size;
                     const size_t vat = ((size_t)page * p.n_v_heads + vh) * p.page_size + kpos % p.page_size;
-                    x = to_float(is_k ? k_pages[at * hd + d] : v_pages[vat * dv + (d - hd)]);
+                    x = to_float(is_k ? k_pages[at * hd + d] : v_pages[vat * p.v_stride + (d - hd)]);
                 }
                 if (is_k) Ks[j * qpitch + d] = x;
                 else Vs[j * dv + (d - hd)] = x;
@@ -192,6 +200,7 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
             const int kpos = u < n_kept ? u : win_lo + (u - n_kept);
             ok[jj] = u < k_hi && kpos <= my_qpos && (p.window <= 0 || kpos > my_qpos - p.window || kpos < p.keep_first);
             s[jj] *= p.scale;
+            if (p.softcap > 0.f) s[jj] = p.softcap * tanhf(s[jj] / p.softcap);
             if (ok[jj] && p.rel != nullptr) s[jj] += p.rel[(size_t)p.bucket[min(my_qpos - kpos, p.n_bucket - 1)] * p.n_heads + my_head];
             if (ok[jj]) tile_max = fmaxf(tile_max, s[jj]);
         }
@@ -236,6 +245,15 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
     if (p.n_splits == 1) {
         T* o = reinterpret_cast<T*>(p.out) + row * dv;
         float* o32 = reinterpret_cast<float*>(p.out) + row * dv;
+        if (p.sinks != nullptr) {
+            // one more term of the denominator: exp(sink - M) with M = max(m, sink), everything else rescaled to M
+            const float sink = p.sinks[head];
+            const float M = fmaxf(m, sink);
+            const float a = expf(m - M);           // m = -inf (no visible key) gives 0
+            l = l * a + expf(sink - M);
+#pragma unroll
+            for (int jd = 0; jd < HD_MAX / 8; ++jd) acc[jd] *= a;
+        }
         float inv = l > 0.f ? 1.f / l : 0.f;
         const T* gate = reinterpret_cast<const T*>(p.gate);
         if (p.gate_mode == 1) inv *= to_float(gate[row]);
@@ -263,11 +281,14 @@ __global__ void __launch_bounds__(NT) paged_attention_kernel(const AttnParams p)
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                        T* __restrict__ out, int n_splits, int head_dim,
-                                       const T* __restrict__ gate, int gate_mode, int out_f32) {
+                                       const T* __restrict__ gate, int gate_mode, int out_f32,
+                                       const float* __restrict__ sinks, int n_heads) {
     const size_t row = blockIdx.x;
     const float* ml = part_ml + row * n_splits * 2;
     float M = -INFINITY;
     for (int i = 0; i < n_splits; ++i) M = fmaxf(M, ml[2 * i]);
+    const float sink = sinks != nullptr ? sinks[row % n_heads] : -INFINITY;
+    M = fmaxf(M, sink);
     for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
         float num = 0.f, den = 0.f;
         for (int i = 0; i < n_splits; ++i) {
@@ -277,6 +298,7 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_o, const f
             num = fmaf(w, part_o[(row * n_splits + i) * head_dim + d], num);
             den = fmaf(w, ml[2 * i + 1], den);
         }
+        if (sinks != nullptr) den += expf(sink - M);
         float o = den > 0.f ? num / den : 0.f;
         if (gate_mode == 1) o *= to_float(gate[row]);
         else if (gate_mode == 2) o *= to_float(gate[row * head_dim + d]);
@@ -350,6 +372,9 @@ struct TlAttentionOptions {
     int gate_mode;          // 0: none, 1: [tokens, n_heads], 2: [tokens, n_heads * v_head_dim]
     int n_v_heads;          // 0: as n_kv_heads; else it divides n_kv_heads, and v_pages has so many heads
     int out_f32;            // 1: out is float32 whatever q's dtype
+    float softcap;          // 0: none
+    const float* sinks;     // [n_heads] or null
+    int v_stride;           // 0: as v_head_dim
 };
 
 // How many key splits the general kernel would use for this batch, and how many float32 words of
@@ -396,6 +421,8 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
     if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;
     if (o.gate_mode < 0 || o.gate_mode > 2 || (o.gate_mode != 0 && o.gate == nullptr)) return TL_BAD_SIZE;
     if (o.n_v_heads <= 0) o.n_v_heads = n_kv_heads;
+    if (o.v_stride <= 0) o.v_stride = o.v_head_dim;
+    if (o.v_stride < o.v_head_dim || o.softcap < 0.f) return TL_BAD_SIZE;
     if (n_kv_heads % o.n_v_heads != 0 || (o.n_v_heads != n_kv_heads && v_pages == k_pages)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return TL_BAD_ALIGN;
     const Plan pl = make_plan(n_seqs, n_heads, n_kv_heads, max_q_len, max_kv_len, allow_split, window, o.keep_first);
@@ -416,6 +443,7 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
     p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
     p.gate = o.gate; p.gate_mode = o.gate_mode;
     p.n_v_heads = o.n_v_heads; p.out_f32 = o.out_f32;
+    p.v_stride = o.v_stride; p.softcap = o.softcap; p.sinks = o.sinks;
     p.n_splits = pl.n_splits;
     p.scale = scale;
     p.part_o = workspace;
@@ -433,10 +461,11 @@ extern "C" int tl_paged_attention_ex(const void* q, const void* k_pages, const v
         const unsigned rows = (unsigned)n_tokens * n_heads;
         if (dtype == TL_F32)
             attention_merge_kernel<float><<<rows, threads, 0, s>>>(p.part_o, p.part_ml, (float*)out, pl.n_splits, o.v_head_dim,
-                                                                    (const float*)o.gate, o.gate_mode, o.out_f32);
+                                                                    (const float*)o.gate, o.gate_mode, o.out_f32, o.sinks, n_heads);
         else
             attention_merge_kernel<__nv_bfloat16><<<rows, threads, 0, s>>>(p.part_o, p.part_ml, (__nv_bfloat16*)out, pl.n_splits,
-                                                                            o.v_head_dim, (const __nv_bfloat16*)o.gate, o.gate_mode, o.out_f32);
+                                                                            o.v_head_dim, (const __nv_bfloat16*)o.gate, o.gate_mode, o.out_f32,
+                                                                            o.sinks, n_heads);
         TL_LAUNCH_CHECK();
     }
     return TL_OK;

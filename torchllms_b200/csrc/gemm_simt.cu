@@ -20,10 +20,12 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W,
                                                        TO* __restrict__ C, int M, int N, int K,
                                                        long long lda, long long ldc, long long a_batch,
-                                                       long long w_batch, long long c_batch) {
+                                                       long long w_batch, long long c_batch,
+                                                       const TO* __restrict__ gate = nullptr, long long ldg = 0, long long g_batch = 0) {
     A += blockIdx.z * a_batch;
     W += blockIdx.z * w_batch;
     C += blockIdx.z * c_batch;
+    if (gate != nullptr) gate += blockIdx.z * g_batch;
     __shared__ float As[BK][BM + PAD];
     __shared__ float Ws[BK][BN + PAD];
     const int tid = threadIdx.x;
@@ -68,18 +70,19 @@ __global__ void __launch_bounds__(NT) gemm_simt_kernel(const T* __restrict__ A, 
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn < N) C[(size_t)gm * ldc + gn] = from_float<TO>(acc[i][j]);
+            if (gn < N) C[(size_t)gm * ldc + gn] = from_float<TO>(gate != nullptr ? acc[i][j] * to_float(gate[(size_t)gm * ldg + gn]) : acc[i][j]);
         }
     }
 }
 
 template <typename T, typename TO>
 int launch(const void* A, const void* W, void* C, int M, int N, int K, cudaStream_t s, int batches = 1,
-           long long lda = -1, long long ldc = -1, long long a_batch = 0, long long w_batch = 0, long long c_batch = 0) {
+           long long lda = -1, long long ldc = -1, long long a_batch = 0, long long w_batch = 0, long long c_batch = 0,
+           const void* gate = nullptr, long long ldg = 0, long long g_batch = 0) {
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM, batches);
     if (grid.y > 65535 || batches > 65535) return TL_BAD_SIZE;
     gemm_simt_kernel<T, TO><<<grid, NT, 0, s>>>((const T*)A, (const T*)W, (TO*)C, M, N, K, lda < 0 ? K : lda,
-                                                ldc < 0 ? N : ldc, a_batch, w_batch, c_batch);
+                                                ldc < 0 ? N : ldc, a_batch, w_batch, c_batch, (const TO*)gate, ldg, g_batch);
     TL_LAUNCH_CHECK();
     return TL_OK;
 }
@@ -103,10 +106,12 @@ namespace {
 // a thread per output column walking that column's K weights 16 bytes at a time where K allows.
 template <typename T>
 __global__ void __launch_bounds__(128) head_linear_rows_kernel(const T* __restrict__ x, const T* __restrict__ w,
-                                                               T* __restrict__ out, int n_heads, int N, int K) {
+                                                               T* __restrict__ out, int n_heads, int N, int K,
+                                                               long long ldx, long long hsx, long long ldo, long long hso,
+                                                               const T* __restrict__ gate) {
     extern __shared__ __align__(16) float xs[];
     const int h = blockIdx.x, t = blockIdx.y;
-    const T* xr = x + ((size_t)t * n_heads + h) * K;
+    const T* xr = x + (size_t)t * ldx + (size_t)h * hsx;
     for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float(xr[k]);
     __syncthreads();
     constexpr int VEC = Vec16<T>::N;
@@ -124,7 +129,8 @@ __global__ void __launch_bounds__(128) head_linear_rows_kernel(const T* __restri
         } else {
             for (int k = 0; k < K; ++k) acc = fmaf(to_float(wr[k]), xs[k], acc);
         }
-        out[((size_t)t * n_heads + h) * N + n] = from_float<T>(acc);
+        if (gate != nullptr) acc *= to_float(gate[((size_t)t * n_heads + h) * N + n]);
+        out[(size_t)t * ldo + (size_t)h * hso + n] = from_float<T>(acc);
     }
 }
 
@@ -132,6 +138,36 @@ __global__ void __launch_bounds__(128) head_linear_rows_kernel(const T* __restri
 
 // One product per head: x [tokens, heads, K] against w [heads, N, K] gives out [tokens, heads, N],
 // out[t, h, :] = w[h] x[t, h, :]; x, w and out have one dtype.
+// The extended form: token t's head h reads x + t * ldx + h * hsx (K numbers) and writes out + t * ldo + h * hso
+// (N numbers), so either may be a part of every head of wider rows; gate ([tokens, heads, N], dense, or null)
+// multiplies the result.
+extern "C" int tl_head_linear_ex(const void* x, const void* w, void* out, const void* gate, int dtype, int n_tokens, int n_heads,
+                                 int N, int K, long long ldx, long long hsx, long long ldo, long long hso, void* stream) {
+    if (n_tokens <= 0 || n_heads <= 0 || N <= 0) return TL_OK;
+    if (K <= 0) return TL_BAD_SIZE;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (n_tokens <= 16 && n_heads <= 65535 && (size_t)K * sizeof(float) <= 48 * 1024) {
+        const dim3 grid(n_heads, n_tokens);
+        if (dtype == TL_F32)
+            head_linear_rows_kernel<float><<<grid, 128, (size_t)K * sizeof(float), s>>>((const float*)x, (const float*)w, (float*)out,
+                                                                                         n_heads, N, K, ldx, hsx, ldo, hso, (const float*)gate);
+        else if (dtype == TL_BF16)
+            head_linear_rows_kernel<__nv_bfloat16><<<grid, 128, (size_t)K * sizeof(float), s>>>(
+                (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n_heads, N, K, ldx, hsx, ldo, hso,
+                (const __nv_bfloat16*)gate);
+        else
+            return TL_BAD_DTYPE;
+        TL_LAUNCH_CHECK();
+        return TL_OK;
+    }
+    const long long ldg = (long long)n_heads * N;
+    if (dtype == TL_F32)
+        return launch<float, float>(x, w, out, n_tokens, N, K, s, n_heads, ldx, ldo, hsx, (long long)N * K, hso, gate, ldg, N);
+    if (dtype == TL_BF16)
+        return launch<__nv_bfloat16, __nv_bfloat16>(x, w, out, n_tokens, N, K, s, n_heads, ldx, ldo, hsx, (long long)N * K, hso, gate, ldg, N);
+    return TL_BAD_DTYPE;
+}
+
 extern "C" int tl_head_linear(const void* x, const void* w, void* out, int dtype, int n_tokens, int n_heads,
                               int N, int K, void* stream) {
     if (n_tokens <= 0 || n_heads <= 0 || N <= 0) return TL_OK;
@@ -141,10 +177,11 @@ extern "C" int tl_head_linear(const void* x, const void* w, void* out, int dtype
         const dim3 grid(n_heads, n_tokens);
         if (dtype == TL_F32)
             head_linear_rows_kernel<float><<<grid, 128, (size_t)K * sizeof(float), s>>>((const float*)x, (const float*)w, (float*)out,
-                                                                                         n_heads, N, K);
+                                                                                         n_heads, N, K, (long long)n_heads * K, K, (long long)n_heads * N, N, nullptr);
         else if (dtype == TL_BF16)
             head_linear_rows_kernel<__nv_bfloat16><<<grid, 128, (size_t)K * sizeof(float), s>>>(
-                (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n_heads, N, K);
+                (const __nv_bfloat16*)x, (const __nv_bfloat16*)w, (__nv_bfloat16*)out, n_heads, N, K, (long long)n_heads * K, K,
+                (long long)n_heads * N, N, nullptr);
         else
             return TL_BAD_DTYPE;
         TL_LAUNCH_CHECK();

@@ -28,6 +28,7 @@ struct ConvParams {
     const void* x;           // [T] rows of pitch ldx, C channels used
     long long ldx;
     const float* w;          // [C][taps], the last column the current token's
+    const float* bias;       // [C] or null: added to the sum before the activation
     float* state;            // [slots] rows of pitch state_pitch, each [taps - 1][C]; null with taps == 1
     long long state_pitch;
     const int* q_start;      // [B + 1]
@@ -68,10 +69,11 @@ __global__ void __launch_bounds__(NT) short_conv_kernel(const ConvParams p) {
 #pragma unroll
     for (int j = 0; j < MAX_TAPS; ++j) w[j] = j < p.taps ? p.w[(size_t)c * p.taps + j] : 0.f;
     TO* out = reinterpret_cast<TO*>(p.out);
+    const float cb = p.bias != nullptr ? p.bias[c] : 0.f;
 #pragma unroll
     for (int i = 0; i < CONV_TOKENS; ++i) {
         if (i < n) {
-            float acc = 0.f;
+            float acc = cb;
 #pragma unroll
             for (int j = 0; j < MAX_TAPS; ++j)
                 if (j < p.taps) acc = fmaf(w[j], in[i + j], acc);
@@ -397,8 +399,9 @@ __global__ void __launch_bounds__(NT) linear_recurrence_kernel(const RecurrenceP
 
 // x: [n_tokens] rows of pitch ldx (elements of in_dtype), `channels` used; w: float32 [channels][taps]; state: float32
 // rows of pitch state_pitch per slot, [taps - 1][channels] each (null with taps == 1); out: [n_tokens][channels].
-// act: 0 none, 1 silu.  residual: x_t is added to the sum before the activation.
-extern "C" int tl_short_conv(const void* x, int in_dtype, long long ldx, const float* w, float* state, long long state_pitch,
+// act: 0 none, 1 silu.  residual: x_t is added to the sum before the activation.  bias: float32 [channels] or null,
+// added to the sum as well.
+extern "C" int tl_short_conv(const void* x, int in_dtype, long long ldx, const float* w, const float* bias, float* state, long long state_pitch,
                              const int* q_start, const int* state_slot, const int* fresh, void* out, int out_dtype,
                              int n_tokens, int n_seqs, int channels, int taps, int max_q_len, int act, int residual,
                              void* stream) {
@@ -406,7 +409,7 @@ extern "C" int tl_short_conv(const void* x, int in_dtype, long long ldx, const f
     if (channels <= 0 || taps < 1 || taps > MAX_TAPS || max_q_len <= 0 || n_seqs > 65535 || act < 0 || act > 1) return TL_BAD_SIZE;
     if (taps > 1 && state == nullptr) return TL_BAD_SIZE;
     ConvParams p;
-    p.x = x; p.ldx = ldx; p.w = w; p.state = taps > 1 ? state : nullptr; p.state_pitch = state_pitch;
+    p.x = x; p.ldx = ldx; p.w = w; p.bias = bias; p.state = taps > 1 ? state : nullptr; p.state_pitch = state_pitch;
     p.q_start = q_start; p.state_slot = state_slot; p.fresh = fresh; p.out = out;
     p.C = channels; p.taps = taps; p.act = act; p.residual = residual;
     p.n_chunks = (max_q_len + CONV_TOKENS - 1) / CONV_TOKENS;

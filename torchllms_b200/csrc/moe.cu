@@ -2,9 +2,11 @@
 //
 // logits:   z = W_router x (float32; W_router may carry one more row, the shared expert's gate), a warp per
 //           (token, row) for the few tokens of a decode step
-// select:   s = softmax(z) over the experts, the `top` experts with the largest s + correction
-//           are chosen (the lower index wins a tie), their weights are s * scale (divided by their
-//           sum first when renormalising); the extra row leaves as sigmoid(z).
+// select:   s = softmax(z) over the experts (or sigmoid(z), each expert by itself), the `top` experts with the
+//           largest s + correction are chosen (the lower index wins a tie), their weights are s * scale
+//           (divided by their sum + renorm_eps first when renormalising); the extra row leaves as sigmoid(z).
+//           With groups the experts form n_groups equal groups of neighbours, a group's score is the sum of
+//           its group_top largest s + correction, and only experts of the keep_groups best groups can be chosen.
 // plan:     the (token, choice) pairs sorted by expert, stably: for every expert where its rows
 //           start, the sorted order and its inverse, and the list of row tiles (expert, first
 //           row, rows) that the grouped products walk.  One CTA; nothing goes back to the host,
@@ -18,7 +20,10 @@
 
 namespace {
 
-enum : int { ACT_NONE = -1, ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2 };
+enum : int { ACT_NONE = -1, ACT_SILU = 0, ACT_GELU_TANH = 1, ACT_RELU2 = 2, ACT_CLAMPED_SWISH = 3 };
+
+// the gated forms: act(gate) * up, or, clamped: g * sigmoid(alpha g) * (u + offset) with g = min(gate, limit), u = clamp(up, +-limit)
+struct GateParams { float limit, alpha, up_offset; };
 
 __device__ __forceinline__ float act_apply(float x, int act) {
     if (act == ACT_NONE) return x;
@@ -26,6 +31,14 @@ __device__ __forceinline__ float act_apply(float x, int act) {
     if (act == ACT_GELU_TANH) return 0.5f * x * (1.f + tanhf(0.7978845608028654f * (x + 0.044715f * x * x * x)));
     const float r = fmaxf(x, 0.f);
     return r * r;
+}
+
+__device__ __forceinline__ float gated_apply(float gate, float up, int act, const GateParams& gp) {
+    if (act == ACT_CLAMPED_SWISH) {
+        const float g = fminf(gate, gp.limit), u = fminf(fmaxf(up, -gp.limit), gp.limit);
+        return g / (1.f + expf(-gp.alpha * g)) * (u + gp.up_offset);
+    }
+    return act_apply(gate, act) * up;
 }
 
 // Router logits of few tokens: grid (tokens, chunks of rows); the token's row in shared memory as float32,
@@ -69,7 +82,8 @@ __global__ void __launch_bounds__(256) moe_logits_kernel(const T* __restrict__ x
 __global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict__ logits, const float* __restrict__ correction,
                                                          const float* __restrict__ logit_bias, int* __restrict__ chosen, float* __restrict__ weights,
                                                          float* __restrict__ gate, int n_tokens, int n_experts, int n_rows,
-                                                         int top, float scale, int renormalize) {
+                                                         int top, float scale, int renormalize, int sigmoid_scores,
+                                                         int n_groups, int keep_groups, int group_top, float renorm_eps) {
     extern __shared__ float sm[];
     grid_launch_dependents();
     grid_dependency_wait();
@@ -92,12 +106,54 @@ __global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict
     sum = warp_sum(sum);
     const float inv = 1.f / sum;
     for (int e = lane; e < n_experts; e += 32) {
-        const float s = expf(ch[e] - mx) * inv;
+        const float s = sigmoid_scores ? 1.f / (1.f + expf(-ch[e])) : expf(ch[e] - mx) * inv;
         sc[e] = s;
         ch[e] = s + (correction != nullptr ? correction[e] : 0.f);
     }
     if (lane == 0 && gate != nullptr) gate[t] = 1.f / (1.f + expf(-z[n_experts]));
     __syncwarp();
+    if (n_groups > 1) {
+        // a lane per group (in turns): the sum of the group's group_top largest values; then the best groups are
+        // marked one by one (the lower index wins a tie) and the experts of all others leave the choice
+        const int per = n_experts / n_groups;
+        float* gsc = sm + (size_t)(blockDim.x >> 5) * 2 * n_experts + (size_t)warp * n_groups;
+        for (int g = lane; g < n_groups; g += 32) {
+            float total_g = 0.f;
+            float below = INFINITY;        // values are taken in falling order: (value, index) strictly after the last taken
+            int below_at = -1;
+            for (int k = 0; k < group_top && k < per; ++k) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int e = 0; e < per; ++e) {
+                    const float v = ch[g * per + e];
+                    const bool after = v < below || (v == below && e > below_at);
+                    if (after && v > best) { best = v; at = e; }
+                }
+                if (at < 0) break;
+                total_g += best;
+                below = best;
+                below_at = at;
+            }
+            gsc[g] = total_g;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            // keep_groups rounds of selection; a kept group's score becomes +inf so that it is told from the rest below
+            for (int k = 0; k < keep_groups; ++k) {
+                float best = -INFINITY;
+                int at = -1;
+                for (int g = 0; g < n_groups; ++g) {
+                    const float v = gsc[g];
+                    if (v != INFINITY && (at < 0 || v > best)) { best = v; at = g; }
+                }
+                if (at >= 0) gsc[at] = INFINITY;
+            }
+        }
+        __syncwarp();
+        for (int e = lane; e < n_experts; e += 32)
+            if (gsc[e / per] != INFINITY) ch[e] = -INFINITY;
+        __syncwarp();
+    }
     float total = 0.f;
     for (int k = 0; k < top; ++k) {
         float best = -INFINITY;
@@ -122,7 +178,7 @@ __global__ void __launch_bounds__(128) moe_select_kernel(const float* __restrict
         __syncwarp();
     }
     if (lane == 0) {
-        const float f = renormalize ? scale / total : scale;
+        const float f = renormalize ? scale / (total + renorm_eps) : scale;
         for (int k = 0; k < top; ++k) weights[(size_t)t * top + k] *= f;
     }
 }
@@ -334,7 +390,8 @@ __global__ void moe_gather_kernel(const T* __restrict__ x, const int* __restrict
 template <typename TI, typename TO>
 __global__ void moe_scale_act_kernel(const TI* __restrict__ u, int splits, long long plane, const int* __restrict__ chosen,
                                      const float* __restrict__ weights, const float* __restrict__ gate, TO* __restrict__ out,
-                                     int n_experts, int hidden, int extra, int top, int act, int gated) {
+                                     int n_experts, int hidden, int extra, int top, int act, int gated, GateParams gp,
+                                     GateParams gp_extra) {
     extern __shared__ float wexp[];      // [n_experts]: this token's weight per expert
     grid_launch_dependents();
     grid_dependency_wait();
@@ -345,19 +402,22 @@ __global__ void moe_scale_act_kernel(const TI* __restrict__ u, int splits, long 
     __syncthreads();
     const float g = gate != nullptr ? gate[t] : 1.f;
     if (gated) {
-        // an expert's columns of u are [gate | up], hidden each; out has hidden columns per expert: act(gate) * up * weight
+        // an expert's columns of u are [gate | up], hidden each, and after all experts a shared expert's [gate | up], extra
+        // each; out has hidden columns per expert, gated(gate, up) * weight, and extra more, gated(gate, up) * g
         for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < width; c += gridDim.y * blockDim.x) {
-            const int e = c / hidden, f = c - e * hidden;
-            const float w = wexp[e];
+            const bool own = c < n_experts * hidden;
+            const int e = own ? c / hidden : n_experts, f = own ? c - e * hidden : c - n_experts * hidden;
+            const float w = own ? wexp[e] : g;
             float v = 0.f;
             if (w != 0.f) {
                 const size_t at = (size_t)t * 2 * width + (size_t)e * 2 * hidden + f;
+                const int up_at = own ? hidden : extra;
                 float a = 0.f, b = 0.f;
                 for (int sp = 0; sp < splits; ++sp) {
                     a += to_float(u[(size_t)sp * plane + at]);
-                    b += to_float(u[(size_t)sp * plane + at + hidden]);
+                    b += to_float(u[(size_t)sp * plane + at + up_at]);
                 }
-                v = act_apply(a, act) * b * w;
+                v = gated_apply(a, b, act, own ? gp : gp_extra) * w;
             }
             out[(size_t)t * width + c] = from_float<TO>(v);
         }
@@ -387,14 +447,17 @@ extern "C" int tl_moe_gather(const void* x, int dtype, const int* order, void* o
 }
 
 // u: [splits][n_tokens][n_experts * hidden + extra] of in_dtype; out: the same row shape in out_dtype.  gated != 0
-// (extra == 0): u is [splits][n_tokens][n_experts * 2 * hidden], an expert's columns [gate | up], and out
-// [n_tokens][n_experts * hidden] holds act(gate) * up * weight.
+// u is [splits][n_tokens][n_experts * 2 * hidden + 2 * extra], an expert's columns [gate | up] and last a shared
+// expert's [gate | up], and out [n_tokens][n_experts * hidden + extra] holds gated(gate, up) * weight (or * gate[t]).
+// act 3 (gated only): the clamped form with (limit, alpha, up_offset) for the experts and extra_limit for the extra columns.
 extern "C" int tl_moe_scale_act(const void* u, int in_dtype, int splits, long long plane, const int* chosen, const float* weights,
                                 const float* gate, void* out, int out_dtype, int n_tokens, int n_experts, int hidden, int extra,
-                                int top, int act, int gated, void* stream) {
+                                int top, int act, int gated, float limit, float alpha, float up_offset, float extra_limit,
+                                void* stream) {
     if (n_tokens <= 0) return TL_OK;
-    if (gated && extra != 0) return TL_BAD_SIZE;
-    if (n_experts <= 0 || hidden <= 0 || extra < 0 || top <= 0 || top > 1024 || splits < 1 || act < -1 || act > 2) return TL_BAD_SIZE;
+    if (n_experts <= 0 || hidden <= 0 || extra < 0 || top <= 0 || top > 1024 || splits < 1 || act < -1 || act > 3) return TL_BAD_SIZE;
+    if (act == ACT_CLAMPED_SWISH && !gated) return TL_BAD_SIZE;
+    const GateParams gp = {limit, alpha, up_offset}, gp_extra = {extra_limit, alpha, up_offset};
     const size_t smem = (size_t)n_experts * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
     const int width = n_experts * hidden + extra;
@@ -404,7 +467,7 @@ extern "C" int tl_moe_scale_act(const void* u, int in_dtype, int splits, long lo
     cudaStream_t s = (cudaStream_t)stream;
 #define TL_MOE_SA(TI, TO)                                                                                             \
     tl_launch(moe_scale_act_kernel<TI, TO>, grid, block, smem, s, (const TI*)u, splits, plane, chosen, weights, gate, (TO*)out, \
-              n_experts, hidden, extra, top, act, gated)
+              n_experts, hidden, extra, top, act, gated, gp, gp_extra)
     if (in_dtype == TL_F32 && out_dtype == TL_F32) return (int)TL_MOE_SA(float, float);
     if (in_dtype == TL_F32 && out_dtype == TL_BF16) return (int)TL_MOE_SA(float, __nv_bfloat16);
     if (in_dtype == TL_BF16 && out_dtype == TL_BF16) return (int)TL_MOE_SA(__nv_bfloat16, __nv_bfloat16);
@@ -431,15 +494,22 @@ extern "C" int tl_moe_logits(const void* x, int dtype, const float* w_router, fl
 // logits: float32 [n_tokens][n_rows], n_rows = n_experts (+ 1 with gate != null: the shared expert's gate);
 // correction, logit_bias (added to the logits before anything else): float32 [n_experts] or null; chosen: int32 [n_tokens][top]; weights: float32 [n_tokens][top];
 // gate: float32 [n_tokens] or null.
+// sigmoid_scores != 0: every expert's score is the sigmoid of its own logit.  n_groups > 1: see the top of this file
+// (n_groups divides n_experts; keep_groups * n_experts / n_groups >= top).
 extern "C" int tl_moe_select(const float* logits, const float* correction, const float* logit_bias, int* chosen, float* weights,
-                             float* gate, int n_tokens, int n_experts, int top, float scale, int renormalize, void* stream) {
+                             float* gate, int n_tokens, int n_experts, int top, float scale, int renormalize, int sigmoid_scores,
+                             int n_groups, int keep_groups, int group_top, float renorm_eps, void* stream) {
     if (n_tokens <= 0) return TL_OK;
     if (n_experts <= 0 || top <= 0 || top > n_experts) return TL_BAD_SIZE;
+    if (n_groups < 1 || n_experts % n_groups != 0 || keep_groups < 1 || keep_groups > n_groups || group_top < 1 ||
+        (long long)keep_groups * (n_experts / n_groups) < top)
+        return TL_BAD_SIZE;
     const int n_rows = n_experts + (gate != nullptr ? 1 : 0);
-    const size_t smem = (size_t)4 * 2 * n_experts * sizeof(float);
+    const size_t smem = (size_t)4 * (2 * n_experts + n_groups) * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
     return (int)tl_launch(moe_select_kernel, dim3((n_tokens + 3) / 4), dim3(128), smem, (cudaStream_t)stream, logits, correction,
-                          logit_bias, chosen, weights, gate, n_tokens, n_experts, n_rows, top, scale, renormalize);
+                          logit_bias, chosen, weights, gate, n_tokens, n_experts, n_rows, top, scale, renormalize, sigmoid_scores,
+                          n_groups, keep_groups, group_top, renorm_eps);
 }
 
 // rows of a tile for this many (token, choice) pairs, and how many tiles there can be at most

@@ -236,7 +236,7 @@ extern "C" int tl_rope_kv_write(const void* qkv, int in_dtype, int splits, const
 // sigmoids (gates that ride in the same projection).  k_pages: [pages, n_k_heads, page_size,
 // head_dim]; v_pages: [pages, n_v_heads, page_size, v_head_dim].  One CTA per token.
 template <typename TI, typename T>
-__global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long long plane,
+__global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long long plane, const float* __restrict__ bias,
                                   const int* __restrict__ positions, const float* __restrict__ table,
                                   const int* __restrict__ slot_mapping, T* __restrict__ q_out, T* __restrict__ extra_out,
                                   T* __restrict__ k_pages, T* __restrict__ v_pages, int n_q_heads, int n_k_heads,
@@ -263,7 +263,7 @@ __global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long 
         if (!(TL_CHECK(sm >= 0, TL_DBG_SLOT) && tl_check_page(page))) write = false;
     }
     auto value = [&](int c) {
-        float x = 0.f;
+        float x = bias != nullptr ? bias[c] : 0.f;
         for (int sp = 0; sp < splits; ++sp) x += to_float(src[(size_t)sp * plane + c]);
         return x;
     };
@@ -301,8 +301,8 @@ __global__ void rope_store_kernel(const TI* __restrict__ proj, int splits, long 
 // proj: [splits, n_tokens, width] of in_dtype, width = (n_q_heads + n_k_heads) * head_dim + n_v_heads * v_head_dim
 // + n_extra; n_k_heads = n_v_heads = 0 for a run that reads another run's cache (pages may then be null);
 // table: float32 [table_rows, rot_dims / 2, 2]; q_out [n_tokens, n_q_heads, head_dim], extra_out [n_tokens, n_extra]
-// and the pages in dtype.
-extern "C" int tl_rope_store(const void* proj, int in_dtype, int splits, const int* positions, const float* table,
+// and the pages in dtype.  bias: float32 [width] or null, added to the row before anything else.
+extern "C" int tl_rope_store(const void* proj, int in_dtype, int splits, const float* bias, const int* positions, const float* table,
                              const int* slot_mapping, void* q_out, void* extra_out, void* k_pages, void* v_pages, int dtype,
                              int n_tokens, int n_q_heads, int n_k_heads, int n_v_heads, int head_dim, int v_head_dim,
                              int rot_dims, int n_extra, int page_size, int table_rows, int interleaved, void* stream) {
@@ -323,12 +323,161 @@ extern "C" int tl_rope_store(const void* proj, int in_dtype, int splits, const i
     }
     cudaStream_t s = (cudaStream_t)stream;
 #define TL_ROPE_STORE(TI, T)                                                                                          \
-    tl_launch(rope_store_kernel<TI, T>, dim3(n_tokens, by), dim3(threads), 0, s, (const TI*)proj, splits, plane, positions, \
+    tl_launch(rope_store_kernel<TI, T>, dim3(n_tokens, by), dim3(threads), 0, s, (const TI*)proj, splits, plane, bias, positions, \
               table, slot_mapping, (T*)q_out, (T*)extra_out, (T*)k_pages, (T*)v_pages, n_q_heads, n_k_heads, n_v_heads, \
               head_dim, v_head_dim, rot_dims, n_extra, page_size, table_rows, interleaved)
     if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_ROPE_STORE(float, float);
     if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_ROPE_STORE(__nv_bfloat16, __nv_bfloat16);
     if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_ROPE_STORE(float, __nv_bfloat16);
 #undef TL_ROPE_STORE
+    return TL_BAD_DTYPE;
+}
+
+// ---------------------------------------------------------------------------------------------
+// What follows the stacked input projection of a latent-attention mixer whose row is
+// [q latent | kv latent | rotated key part | extra]: both latents are RMS-normed under weights of their own
+// (float32), the key part (all of its n_rot coordinates) is rotated by the position, [kv latent | key part]
+// goes into the token's place of the one-headed pages ([pages, 1, page_size, n_latent + n_rot]), and the normed
+// q latent and the sigmoids of the extra columns leave as tensors.  One CTA per token; the row is summed
+// over the split-K planes twice (for the sums of squares, then for the results), which costs less than
+// keeping it.
+namespace {
+
+__device__ __forceinline__ float block_sum_2(float v, float* part) {      // part: 33 floats of shared memory
+    v = warp_sum(v);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    __syncthreads();
+    if (lane == 0) part[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? part[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) part[32] = t;
+    }
+    __syncthreads();
+    return part[32];
+}
+
+template <typename TI, typename T>
+__global__ void latent_store_kernel(const TI* __restrict__ proj, int splits, long long plane, const int* __restrict__ positions,
+                                    const float* __restrict__ table, const int* __restrict__ slot_mapping,
+                                    const float* __restrict__ q_norm, const float* __restrict__ latent_norm, float eps,
+                                    T* __restrict__ q_out, T* __restrict__ extra_out, T* __restrict__ pages, int n_q, int n_latent,
+                                    int n_rot, int n_extra, int page_size, int table_rows, int interleaved) {
+    __shared__ float part[33];
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int t = blockIdx.x;
+    const int width = n_q + n_latent + n_rot + n_extra;
+    const TI* src = proj + (size_t)t * width;
+    auto value = [&](int c) {
+        float x = 0.f;
+        for (int sp = 0; sp < splits; ++sp) x += to_float(src[(size_t)sp * plane + c]);
+        return x;
+    };
+    float sq = 0.f, sc = 0.f;
+    for (int c = threadIdx.x; c < n_q + n_latent; c += blockDim.x) {
+        const float v = value(c);
+        if (c < n_q) sq = fmaf(v, v, sq);
+        else sc = fmaf(v, v, sc);
+    }
+    const float rq = n_q > 0 ? rsqrtf(block_sum_2(sq, part) / (float)n_q + eps) : 0.f;
+    const float rc = rsqrtf(block_sum_2(sc, part) / (float)n_latent + eps);
+    int pos = positions[t];
+    (void)TL_CHECK(pos >= 0 && pos < table_rows, TL_DBG_POSITION);
+    pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
+    const float* cs = table + (size_t)pos * n_rot;      // [n_rot / 2][2]
+    const int sm = slot_mapping[t];
+    const int page = sm / page_size, slot = sm - page * page_size;
+    const bool write = pages != nullptr && TL_CHECK(sm >= 0, TL_DBG_SLOT) && tl_check_page(page);
+    T* dst = pages + ((size_t)page * page_size + slot) * (n_latent + n_rot);
+    for (int c = threadIdx.x; c < n_q; c += blockDim.x) q_out[(size_t)t * n_q + c] = from_float<T>(value(c) * rq * q_norm[c]);
+    if (write) {
+        for (int c = threadIdx.x; c < n_latent; c += blockDim.x) dst[c] = from_float<T>(value(n_q + c) * rc * latent_norm[c]);
+        const int half = n_rot >> 1;
+        for (int i = threadIdx.x; i < half; i += blockDim.x) {
+            const int l0 = interleaved ? 2 * i : i, l1 = interleaved ? 2 * i + 1 : i + half;
+            const float x0 = value(n_q + n_latent + l0), x1 = value(n_q + n_latent + l1);
+            const float c = cs[2 * i], s = cs[2 * i + 1];
+            dst[n_latent + l0] = from_float<T>(x0 * c - x1 * s);
+            dst[n_latent + l1] = from_float<T>(x1 * c + x0 * s);
+        }
+    }
+    for (int c = threadIdx.x; c < n_extra; c += blockDim.x)
+        extra_out[(size_t)t * n_extra + c] = from_float<T>(1.f / (1.f + expf(-value(n_q + n_latent + n_rot + c))));
+}
+
+// out[t, h, o_off + d] = the first `rot` coordinates from x[t, h, x_off ...] rotated by the token's position; a thread per pair
+template <typename T>
+__global__ void rope_segment_kernel(const T* __restrict__ x, long long ldx, long long hsx, T* __restrict__ out, long long ldo,
+                                    long long hso, const int* __restrict__ positions, const float* __restrict__ table,
+                                    int table_rows, long long total, int n_heads, int rot, int interleaved) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    const int half = rot >> 1;
+    for (long long w = (long long)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += (long long)gridDim.x * blockDim.x) {
+        const int i = (int)(w % half);
+        const long long th = w / half;
+        const int h = (int)(th % n_heads);
+        const long long t = th / n_heads;
+        int pos = positions[t];
+        (void)TL_CHECK(pos >= 0 && pos < table_rows, TL_DBG_POSITION);
+        pos = pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
+        const float c = table[((size_t)pos * half + i) * 2], s = table[((size_t)pos * half + i) * 2 + 1];
+        const int l0 = interleaved ? 2 * i : i, l1 = interleaved ? 2 * i + 1 : i + half;
+        const T* src = x + t * ldx + h * hsx;
+        T* dst = out + t * ldo + h * hso;
+        const float x0 = to_float(src[l0]), x1 = to_float(src[l1]);
+        dst[l0] = from_float<T>(x0 * c - x1 * s);
+        dst[l1] = from_float<T>(x1 * c + x0 * s);
+    }
+}
+
+}  // namespace
+
+// proj: [splits, n_tokens, n_q + n_latent + n_rot + n_extra] of in_dtype; table: float32 [table_rows, n_rot / 2, 2];
+// q_norm [n_q], latent_norm [n_latent]: float32; q_out [n_tokens, n_q], extra_out [n_tokens, n_extra] and pages
+// [pages, 1, page_size, n_latent + n_rot] in dtype.
+extern "C" int tl_latent_store(const void* proj, int in_dtype, int splits, const int* positions, const float* table,
+                               const int* slot_mapping, const float* q_norm, const float* latent_norm, float eps, void* q_out,
+                               void* extra_out, void* pages, int dtype, int n_tokens, int n_q, int n_latent, int n_rot,
+                               int n_extra, int page_size, int table_rows, int interleaved, void* stream) {
+    if (n_tokens <= 0) return TL_OK;
+    if (n_q < 0 || n_latent <= 0 || n_rot < 0 || (n_rot & 1) || n_extra < 0 || splits < 1 || page_size <= 0 || table_rows <= 0)
+        return TL_BAD_SIZE;
+    if ((n_extra > 0 && extra_out == nullptr) || (n_q > 0 && (q_out == nullptr || q_norm == nullptr)) || slot_mapping == nullptr)
+        return TL_BAD_SIZE;
+    const long long width = (long long)n_q + n_latent + n_rot + n_extra;
+    const long long plane = (long long)n_tokens * width;
+    const int threads = width >= 2048 ? 256 : 128;
+    cudaStream_t s = (cudaStream_t)stream;
+#define TL_LATENT_STORE(TI, T)                                                                                              \
+    tl_launch(latent_store_kernel<TI, T>, dim3(n_tokens), dim3(threads), 0, s, (const TI*)proj, splits, plane, positions, table, \
+              slot_mapping, q_norm, latent_norm, eps, (T*)q_out, (T*)extra_out, (T*)pages, n_q, n_latent, n_rot, n_extra,      \
+              page_size, table_rows, interleaved)
+    if (in_dtype == TL_F32 && dtype == TL_F32) return (int)TL_LATENT_STORE(float, float);
+    if (in_dtype == TL_BF16 && dtype == TL_BF16) return (int)TL_LATENT_STORE(__nv_bfloat16, __nv_bfloat16);
+    if (in_dtype == TL_F32 && dtype == TL_BF16) return (int)TL_LATENT_STORE(float, __nv_bfloat16);
+#undef TL_LATENT_STORE
+    return TL_BAD_DTYPE;
+}
+
+// x, out: [n_tokens] rows of pitches ldx, ldo (elements), every head hsx, hso further on; the pointers name the first
+// rotated coordinate of head 0 of token 0.  table: float32 [table_rows, rot / 2, 2].
+extern "C" int tl_rope_segment(const void* x, long long ldx, long long hsx, void* out, long long ldo, long long hso, int dtype,
+                               const int* positions, const float* table, int table_rows, int n_tokens, int n_heads, int rot,
+                               int interleaved, void* stream) {
+    if (n_tokens <= 0 || n_heads <= 0 || rot == 0) return TL_OK;
+    if (rot < 0 || (rot & 1) || table_rows <= 0) return TL_BAD_SIZE;
+    const long long total = (long long)n_tokens * n_heads * (rot / 2);
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TL_F32)
+        return (int)tl_launch(rope_segment_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, (const float*)x, ldx, hsx, (float*)out,
+                              ldo, hso, positions, table, table_rows, total, n_heads, rot, interleaved);
+    if (dtype == TL_BF16)
+        return (int)tl_launch(rope_segment_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)x, ldx,
+                              hsx, (__nv_bfloat16*)out, ldo, hso, positions, table, table_rows, total, n_heads, rot, interleaved);
     return TL_BAD_DTYPE;
 }

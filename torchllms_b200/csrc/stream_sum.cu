@@ -7,6 +7,8 @@
 //             by element; one pass gathers the three sums of squares, one writes.
 // side_gate:  gelu_tanh(u) * table[token]: the gate of a per-token input.
 //
+// stream_inject: h[t] += e[t] + r: a second stream and one row for all tokens (either may be absent), float32.
+//
 // sum_partials: the planes of a split-K product added up and rounded once (for readers that take no partial sums).
 //
 // Sums, norms and the stream are float32 whatever the terms' dtype.  Every term may arrive as float32 partial sums
@@ -138,6 +140,18 @@ __global__ void side_gate_kernel(const TI* __restrict__ u, int splits, long long
     }
 }
 
+__global__ void stream_inject_kernel(float* __restrict__ h, const float* __restrict__ rows, const float* __restrict__ row,
+                                     long long total, int width) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        float v = h[i];
+        if (rows != nullptr) v += rows[i];
+        if (row != nullptr) v += row[i % width];
+        h[i] = v;
+    }
+}
+
 template <typename TO>
 __global__ void sum_partials_kernel(const float* __restrict__ parts, int splits, long long plane, TO* __restrict__ out, long long total) {
     grid_launch_dependents();
@@ -236,4 +250,13 @@ extern "C" int tl_sum_partials(const float* parts, int splits, long long plane, 
     if (out_dtype == TL_BF16)
         return (int)tl_launch(sum_partials_kernel<__nv_bfloat16>, grid, block, 0, s, parts, splits, plane, (__nv_bfloat16*)out, total);
     return TL_BAD_DTYPE;
+}
+
+// h: float32 [n_tokens][width], updated in place; rows: float32 [n_tokens][width] or null; row: float32 [width] or null
+extern "C" int tl_stream_inject(float* h, const float* rows, const float* row, int n_tokens, int width, void* stream) {
+    if (n_tokens <= 0 || width <= 0) return TL_OK;
+    const long long total = (long long)n_tokens * width;
+    long long blocks = (total + 255) / 256;
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    return (int)tl_launch(stream_inject_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, h, rows, row, total, width);
 }

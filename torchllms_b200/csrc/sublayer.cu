@@ -66,9 +66,17 @@ __global__ void stream_rows_kernel(const float* __restrict__ h, __nv_bfloat16* _
         out[i] = __float2bfloat16_rn(h[i]);
 }
 
+template <typename T>
+__global__ void gate_mul_kernel(const T* __restrict__ x, const T* __restrict__ gate, T* __restrict__ out, long long n) {
+    grid_launch_dependents();
+    grid_dependency_wait();
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x)
+        out[i] = from_float<T>(to_float(x[i]) * to_float(gate[i]));
+}
+
 // One CTA per row.  The summed delta is kept in shared memory between the two passes.
 template <typename TD>
-__global__ void norm_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+__global__ void norm_add_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane, const float* __restrict__ bias,
                                 const float* __restrict__ weight, __nv_bfloat16* __restrict__ rows_out, int dim,
                                 float eps) {
     extern __shared__ __align__(16) float row_buf[];
@@ -78,7 +86,7 @@ __global__ void norm_add_kernel(float* __restrict__ h, const TD* __restrict__ de
     const size_t base = (size_t)blockIdx.x * dim;
     float ssq = 0.f;
     for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-        float v = 0.f;
+        float v = bias != nullptr ? bias[d] : 0.f;
         for (int s = 0; s < splits; ++s) v += to_float(delta[(size_t)s * plane + base + d]);
         row_buf[d] = v;
         ssq = fmaf(v, v, ssq);
@@ -242,7 +250,7 @@ __device__ __forceinline__ float4 sum_planes4(const T* p, int splits, long long 
 }
 
 template <typename TD>
-__global__ void norm_add_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+__global__ void norm_add_vec_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane, const float* __restrict__ bias,
                                     const float* __restrict__ weight, __nv_bfloat16* __restrict__ rows_out, int dim,
                                     float eps) {
     extern __shared__ __align__(16) float row_buf[];
@@ -252,7 +260,8 @@ __global__ void norm_add_vec_kernel(float* __restrict__ h, const TD* __restrict_
     const size_t base = (size_t)blockIdx.x * dim;
     float ssq = 0.f;
     for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
-        const float4 v = sum_planes4(delta + base + d, splits, plane);
+        float4 v = sum_planes4(delta + base + d, splits, plane);
+        if (bias != nullptr) { const float4 bb = ld4(bias + d); v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w; }
         st4(row_buf + d, v);
         ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
     }
@@ -413,8 +422,23 @@ extern "C" int tl_stream_rows(const float* h, void* out, long long n, void* stre
                           (__nv_bfloat16*)out, n);
 }
 
+// out = x * gate element by element (float32 product); x, gate and out of one dtype, n elements
+extern "C" int tl_gate_mul(const void* x, const void* gate, void* out, int dtype, long long n, void* stream) {
+    if (n <= 0) return TL_OK;
+    long long blocks = (n + 255) / 256;
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == TL_F32)
+        return (int)tl_launch(gate_mul_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, s, (const float*)x, (const float*)gate, (float*)out, n);
+    if (dtype == TL_BF16)
+        return (int)tl_launch(gate_mul_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, s, (const __nv_bfloat16*)x,
+                              (const __nv_bfloat16*)gate, (__nv_bfloat16*)out, n);
+    return TL_BAD_DTYPE;
+}
+
 // delta: [splits][n_rows][dim] in delta_dtype, planes `plane` elements apart; rows_out (bfloat16) may be null.
-extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int splits, long long plane,
+// bias: float32 [dim] or null, added to the summed delta before its norm.
+extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int splits, long long plane, const float* bias,
                            const float* weight, void* rows_out, int n_rows, int dim, float eps, void* stream) {
     if (n_rows <= 0) return TL_OK;
     if (dim <= 0 || splits < 1) return TL_BAD_SIZE;
@@ -422,14 +446,14 @@ extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int spl
     if (smem > 200 * 1024) return TL_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
     cudaError_t e;
-    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) &&
+    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) && aligned16(bias) &&
                      (rows_out == nullptr || aligned16(rows_out)) && smem <= 48 * 1024;
     if (vec && delta_dtype == TL_F32)
         return (int)tl_launch(norm_add_vec_kernel<float>, dim3(n_rows), dim3(vec_threads(dim, n_rows)), smem, s, h, (const float*)delta,
-                              splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+                              splits, plane, bias, weight, (__nv_bfloat16*)rows_out, dim, eps);
     if (vec && delta_dtype == TL_BF16)
         return (int)tl_launch(norm_add_vec_kernel<__nv_bfloat16>, dim3(n_rows), dim3(vec_threads(dim, n_rows)), smem, s, h,
-                              (const __nv_bfloat16*)delta, splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+                              (const __nv_bfloat16*)delta, splits, plane, bias, weight, (__nv_bfloat16*)rows_out, dim, eps);
     if (delta_dtype == TL_F32) {
         static int raised = 0;
         if (smem > 48 * 1024 && (int)smem > raised) {
@@ -438,7 +462,7 @@ extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int spl
             raised = (int)smem;
         }
         e = tl_launch(norm_add_kernel<float>, dim3(n_rows), dim3(row_threads(dim)), smem, s, h, (const float*)delta, splits,
-                      plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+                      plane, bias, weight, (__nv_bfloat16*)rows_out, dim, eps);
     } else if (delta_dtype == TL_BF16) {
         static int raised = 0;
         if (smem > 48 * 1024 && (int)smem > raised) {
@@ -447,7 +471,7 @@ extern "C" int tl_norm_add(float* h, const void* delta, int delta_dtype, int spl
             raised = (int)smem;
         }
         e = tl_launch(norm_add_kernel<__nv_bfloat16>, dim3(n_rows), dim3(row_threads(dim)), smem, s, h,
-                      (const __nv_bfloat16*)delta, splits, plane, weight, (__nv_bfloat16*)rows_out, dim, eps);
+                      (const __nv_bfloat16*)delta, splits, plane, bias, weight, (__nv_bfloat16*)rows_out, dim, eps);
     } else {
         return TL_BAD_DTYPE;
     }
@@ -564,7 +588,7 @@ __device__ __forceinline__ float act_apply(float x, int act) {
 
 // One CTA per row; the row is kept in shared memory between the passes.  VEC: four columns per thread and turn.
 template <typename TD, typename TO, bool VEC>
-__global__ void norm_add_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane,
+__global__ void norm_add_norm_kernel(float* __restrict__ h, const TD* __restrict__ delta, int splits, long long plane, const float* __restrict__ bias,
                                      const float* __restrict__ weight, const float* __restrict__ weight2,
                                      TO* __restrict__ out, int dim, float eps, float eps2) {
     extern __shared__ __align__(16) float row_buf[];
@@ -575,13 +599,14 @@ __global__ void norm_add_norm_kernel(float* __restrict__ h, const TD* __restrict
     float ssq = 0.f;
     if (VEC) {
         for (int d = threadIdx.x * 4; d < dim; d += blockDim.x * 4) {
-            const float4 v = sum_planes4(delta + base + d, splits, plane);
+            float4 v = sum_planes4(delta + base + d, splits, plane);
+            if (bias != nullptr) { const float4 bb = ld4(bias + d); v.x += bb.x; v.y += bb.y; v.z += bb.z; v.w += bb.w; }
             st4(row_buf + d, v);
             ssq += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
     } else {
         for (int d = threadIdx.x; d < dim; d += blockDim.x) {
-            float v = 0.f;
+            float v = bias != nullptr ? bias[d] : 0.f;
             for (int s = 0; s < splits; ++s) v += to_float(delta[(size_t)s * plane + base + d]);
             row_buf[d] = v;
             ssq = fmaf(v, v, ssq);
@@ -737,7 +762,7 @@ __global__ void differential_combine_kernel(const float* __restrict__ maps, cons
 }  // namespace
 
 // As tl_norm_add, and out = norm of the new h under weight2 / eps2, in out_dtype.
-extern "C" int tl_norm_add_norm(float* h, const void* delta, int delta_dtype, int splits, long long plane,
+extern "C" int tl_norm_add_norm(float* h, const void* delta, int delta_dtype, int splits, long long plane, const float* bias,
                                 const float* weight, const float* weight2, void* out, int out_dtype, int n_rows, int dim,
                                 float eps, float eps2, void* stream) {
     if (n_rows <= 0) return TL_OK;
@@ -745,7 +770,7 @@ extern "C" int tl_norm_add_norm(float* h, const void* delta, int delta_dtype, in
     const size_t smem = (size_t)dim * sizeof(float);
     if (smem > 200 * 1024) return TL_TOO_LARGE;
     cudaStream_t s = (cudaStream_t)stream;
-    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) &&
+    const bool vec = dim % 4 == 0 && plane % 4 == 0 && aligned16(h) && aligned16(delta) && aligned16(weight) && aligned16(bias) &&
                      aligned16(weight2) && aligned16(out);
     const dim3 grid(n_rows), block(vec ? vec_threads(dim, n_rows) : row_threads(dim));
 #define TL_NAN_LAUNCH(TD, TO, V)                                                                                     \
@@ -758,7 +783,7 @@ extern "C" int tl_norm_add_norm(float* h, const void* delta, int delta_dtype, in
             raised = (int)smem;                                                                                      \
         }                                                                                                            \
         return (int)tl_launch(norm_add_norm_kernel<TD, TO, V>, grid, block, smem, s, h, (const TD*)delta, splits,    \
-                              plane, weight, weight2, (TO*)out, dim, eps, eps2);                                     \
+                              plane, bias, weight, weight2, (TO*)out, dim, eps, eps2);                               \
     } while (0)
 #define TL_NAN_PICK(TD, TO) do { if (vec) TL_NAN_LAUNCH(TD, TO, true); else TL_NAN_LAUNCH(TD, TO, false); } while (0)
     if (delta_dtype == TL_F32 && out_dtype == TL_F32) TL_NAN_PICK(float, float);

@@ -41,7 +41,7 @@ NVCC_FLAGS += os.environ.get("TORCHLLMS_B200_NVCC_FLAGS", "").split()
 # libraries that need more than the CUDA runtime
 EXTRA_LINK: Dict[str, List[str]] = {}
 
-ALL_LIBRARIES = ("elementwise", "sublayer", "rope", "attention", "attention_mma", "attention_decode", "attention_prefill", "gemm_simt", "gemm_tcgen05", "sampling", "recurrent", "moe", "matrix_state", "stream_sum")
+ALL_LIBRARIES = ("elementwise", "sublayer", "rope", "attention", "attention_mma", "attention_decode", "attention_prefill", "gemm_simt", "gemm_tcgen05", "sampling", "recurrent", "moe", "matrix_state", "stream_sum", "selective_scan")
 
 
 class KernelBuildError(RuntimeError):

@@ -291,12 +291,18 @@ class NativeOps:
         ``out_dtype`` (``h`` itself for float32), or, with ``then_weight``, the RMS norm of the new
         stream under that weight and ``then_eps`` (the norm in front of the next sublayer, from
         the same kernel)."""
+        bias = None
         if isinstance(delta, PendingProduct):
-            delta = delta.take(self)
+            # (a product's bias is added where its partial sums are added up: in this kernel)
+            bias = delta.bias
+            delta = self.linear(delta.x, delta.w, partials_ok=True)
         _cuda_contig(h, "residual stream", torch.float32)
         _cuda_contig(weight, "norm weight", torch.float32)
         _cuda_contig(delta, "delta")
         _need(h.dim() == 2 and weight.numel() == h.shape[1], "norm weight must match the stream's width")
+        if bias is not None:
+            _cuda_contig(bias, "bias of the product", torch.float32)
+            _need(bias.numel() == h.shape[1], "the product's bias must match the stream's width")
         _need(delta.dtype in _DT and out_dtype in _DT, "norm_add: float32 or bfloat16")
         T, dim = h.shape
         _need(dim * 4 <= 200 * 1024, f"norm_add keeps a row in shared memory: width {dim} exceeds 51200")
@@ -311,13 +317,13 @@ class NativeOps:
             _need(then_weight.numel() == dim, "the following norm's weight must match the stream's width")
             out = torch.empty((T, dim), dtype=out_dtype, device=h.device)
             rc = self._lib("sublayer").tl_norm_add_norm(
-                _ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane), _ptr(weight), _ptr(then_weight),
+                _ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane), _ptr(bias), _ptr(weight), _ptr(then_weight),
                 _ptr(out), _DT[out_dtype], T, dim, ctypes.c_float(eps), ctypes.c_float(then_eps), _stream())
             _check(rc, "norm_add_norm")
             self.launches += 1
             return out
         rows = None if out_dtype == torch.float32 else torch.empty((T, dim), dtype=out_dtype, device=h.device)
-        rc = self._lib("sublayer").tl_norm_add(_ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane),
+        rc = self._lib("sublayer").tl_norm_add(_ptr(h), _ptr(delta), _DT[delta.dtype], splits, ctypes.c_longlong(plane), _ptr(bias),
                                               _ptr(weight), _ptr(rows), T, dim, ctypes.c_float(eps), _stream())
         _check(rc, "norm_add")
         self.launches += 1
@@ -430,30 +436,158 @@ class NativeOps:
         return q, extra
 
     @_timed
-    def head_linear(self, x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    def head_linear(self, x: torch.Tensor, w: torch.Tensor, gate: Optional[torch.Tensor] = None,
+                    out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """One small product per head: ``x [T, H, K]`` against ``w [H, N, K]`` gives ``[T, H, N]``,
         ``out[t, h] = w[h] @ x[t, h]``: float32 multiply-adds on the CUDA cores (a kernel of its own for
         the few rows of a decode step), except bfloat16 with more than 64 rows, which goes to the library's
-        batched product."""
-        _cuda_contig(x, "head_linear input")
+        batched product.  ``x`` may be the first ``K`` coordinates of every head of wider rows, and ``out`` (given)
+        the first ``N`` of every head of wider rows: views with strides ``(tokens, heads, 1)``.  ``gate``
+        (``[T, H * N]``, x's dtype) multiplies the result element by element."""
         _cuda_contig(w, "head_linear weight", x.dtype)
-        _need(x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2] and x.dtype in _DT,
-              "head_linear: x [T, H, K] against w [H, N, K]")
+        _need(x.is_cuda and x.dim() == 3 and w.dim() == 3 and x.shape[1] == w.shape[0] and x.shape[2] == w.shape[2] and x.dtype in _DT
+              and x.stride(2) == 1, "head_linear: x [T, H, K] against w [H, N, K]")
         T, H, K = x.shape
         N = w.shape[1]
+        if out is None:
+            out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
+        _need(out.is_cuda and out.shape == (T, H, N) and out.dtype == x.dtype and out.stride(2) == 1, "head_linear: out [T, H, N] of x's dtype")
+        if gate is not None:
+            _cuda_contig(gate, "head_linear gate", x.dtype)
+            _need(gate.numel() == T * H * N, "head_linear: one gate value per element of the result")
         if x.dtype == torch.bfloat16 and T > 64:
             # prompt portions: the library's batched product, as linear() does for so many rows
             # (heads are the batch: inputs and result are read and written in place through their strides)
-            out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
             torch.bmm(x.transpose(0, 1), w.transpose(1, 2), out=out.transpose(0, 1))
+            if gate is not None:
+                _need(out.is_contiguous(), "head_linear: a gated result is dense")
+                _check(self._lib("sublayer").tl_gate_mul(_ptr(out), _ptr(gate), _ptr(out), _DT[x.dtype], ctypes.c_longlong(out.numel()),
+                                                        _stream()), "gate_mul")
+                self.launches += 1
             return out
-        out = torch.empty((T, H, N), dtype=x.dtype, device=x.device)
-        _check(self._lib("gemm_simt").tl_head_linear(_ptr(x), _ptr(w), _ptr(out), _DT[x.dtype], T, H, N, K, _stream()), "head_linear")
+        rc = self._lib("gemm_simt").tl_head_linear_ex(
+            _ptr(x), _ptr(w), _ptr(out), _ptr(gate), _DT[x.dtype], T, H, N, K, ctypes.c_longlong(x.stride(0)),
+            ctypes.c_longlong(x.stride(1)), ctypes.c_longlong(out.stride(0)), ctypes.c_longlong(out.stride(1)), _stream())
+        _check(rc, "head_linear")
+        self.launches += 1
+        return out
+
+    @_timed
+    def latent_store(self, proj: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *, n_q: int, n_latent: int, n_rot: int,
+                     n_extra: int, q_norm: torch.Tensor, latent_norm: torch.Tensor, eps: float, interleaved: bool,
+                     k_pages: torch.Tensor, slot_mapping: torch.Tensor, page_size: int, out_dtype: torch.dtype):
+        """What follows the stacked input projection of a latent-attention mixer with a rotated key part, whose rows
+        are ``[q latent | kv latent | key part | extra]`` (``[T, width]`` or float32 partial sums): both latents are
+        RMS-normed under their weights (float32), the key part's ``n_rot`` coordinates are rotated by the position
+        (``table`` float32 ``[positions, n_rot / 2, 2]``), ``[kv latent | key part]`` goes into ``k_pages`` ``[pages, 1,
+        page_size, n_latent + n_rot]`` at ``slot_mapping``, and the normed q latent and ``sigmoid(extra)`` come back."""
+        _cuda_contig(proj, "projection")
+        _cuda_contig(positions, "positions", torch.int32)
+        _cuda_contig(table, "rotary table", torch.float32)
+        _cuda_contig(slot_mapping, "slot_mapping", torch.int32)
+        _cuda_contig(k_pages, "k_pages", out_dtype)
+        _cuda_contig(q_norm, "q_norm", torch.float32)
+        _cuda_contig(latent_norm, "latent_norm", torch.float32)
+        width = n_q + n_latent + n_rot + n_extra
+        _need(proj.dim() in (2, 3) and proj.shape[-1] == width and proj.dtype in _DT, "projection rows must be [q latent | kv latent | key part | extra]")
+        splits = proj.shape[0] if proj.dim() == 3 else 1
+        _need(splits == 1 or proj.dtype == torch.float32, "partial sums must be float32")
+        _need(out_dtype in _DT and (out_dtype == proj.dtype or proj.dtype == torch.float32), "latent_store cannot widen bfloat16 input")
+        _need(n_rot % 2 == 0 and table.dim() == 3 and table.shape[2] == 2 and (n_rot == 0 or table.shape[1] == n_rot // 2),
+              "rotary table must be [positions, n_rot / 2, 2]")
+        _need(q_norm.numel() == n_q and latent_norm.numel() == n_latent, "one norm weight per latent coordinate")
+        T = proj.shape[-2]
+        _need(positions.numel() == T and slot_mapping.numel() == T, "one position and one cache slot per token")
+        _need(k_pages.dim() == 4 and k_pages.shape[1:] == (1, page_size, n_latent + n_rot), "pages must be [pages, 1, page_size, n_latent + n_rot]")
+        self._debug_limit("rope", 0, k_pages.shape[0])
+        q = torch.empty((T, n_q), dtype=out_dtype, device=proj.device)
+        extra = torch.empty((T, n_extra), dtype=out_dtype, device=proj.device) if n_extra else None
+        rc = self._lib("rope").tl_latent_store(
+            _ptr(proj), _DT[proj.dtype], splits, _ptr(positions), _ptr(table), _ptr(slot_mapping), _ptr(q_norm), _ptr(latent_norm),
+            ctypes.c_float(eps), _ptr(q), _ptr(extra), _ptr(k_pages), _DT[out_dtype], T, n_q, n_latent, n_rot, n_extra, page_size,
+            table.shape[0], 1 if interleaved else 0, _stream())
+        _check(rc, "latent_store")
+        self.launches += 1
+        return q, extra
+
+    @_timed
+    def latent_query(self, q: torch.Tensor, w_uk_t: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *, rot_dim: int,
+                     interleaved: bool) -> torch.Tensor:
+        """The queries of absorbed latent attention: ``q [T, H, d + rot_dim]`` and ``w_uk_t [H, rank, d]`` give
+        ``[T, H, rank + rot_dim]`` = ``[w_uk_t[h] @ q[t, h, :d] | q[t, h, d:] rotated by the position]``: a per-head
+        product written into the wider rows, and a rotation kernel for their tails."""
+        _cuda_contig(q, "latent queries")
+        _need(q.dim() == 3 and w_uk_t.dim() == 3 and q.shape[1] == w_uk_t.shape[0] and q.shape[2] == w_uk_t.shape[2] + rot_dim,
+              "latent_query: q [T, H, d + rot_dim] against w_uk_t [H, rank, d]")
+        T, H, qd = q.shape
+        d, rank = qd - rot_dim, w_uk_t.shape[1]
+        out = torch.empty((T, H, rank + rot_dim), dtype=q.dtype, device=q.device)
+        self.head_linear(q[:, :, :d], w_uk_t, out=out[:, :, :rank])
+        if rot_dim:
+            _cuda_contig(positions, "positions", torch.int32)
+            _cuda_contig(table, "rotary table", torch.float32)
+            _need(rot_dim % 2 == 0 and table.dim() == 3 and table.shape[1] == rot_dim // 2 and table.shape[2] == 2 and positions.numel() == T,
+                  "rotary table must be [positions, rot_dim / 2, 2], one position per token")
+            rc = self._lib("rope").tl_rope_segment(
+                ctypes.c_void_p(q.data_ptr() + d * q.element_size()), ctypes.c_longlong(q.stride(0)), ctypes.c_longlong(q.stride(1)),
+                ctypes.c_void_p(out.data_ptr() + rank * out.element_size()), ctypes.c_longlong(out.stride(0)),
+                ctypes.c_longlong(out.stride(1)), _DT[q.dtype], _ptr(positions), _ptr(table), table.shape[0], T, H, rot_dim,
+                1 if interleaved else 0, _stream())
+            _check(rc, "rope_segment")
+            self.launches += 1
+        return out
+
+    @_timed
+    def stream_inject(self, h: torch.Tensor, rows: Optional[torch.Tensor], row: Optional[torch.Tensor]) -> None:
+        """``h += rows + row`` in place (float32): ``rows`` ``[T, dim]`` (another stream, e.g. the embedding output) and
+        ``row`` ``[dim]`` (one vector for every token); either may be ``None``."""
+        _cuda_contig(h, "residual stream", torch.float32)
+        T, dim = h.shape
+        if rows is not None:
+            _cuda_contig(rows, "added stream", torch.float32)
+            _need(rows.shape == h.shape, "the added stream must have the stream's shape")
+        if row is not None:
+            _cuda_contig(row, "added row", torch.float32)
+            _need(row.numel() == dim, "the added row must have the stream's width")
+        if rows is None and row is None:
+            return
+        _check(self._lib("stream_sum").tl_stream_inject(_ptr(h), _ptr(rows), _ptr(row), T, dim, _stream()), "stream_inject")
+        self.launches += 1
+
+    @_timed
+    def selective_scan(self, x: torch.Tensor, dt: torch.Tensor, B: torch.Tensor, C: torch.Tensor, z: torch.Tensor, A: torch.Tensor,
+                       D: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor, q_start: torch.Tensor, state_slot: torch.Tensor,
+                       fresh: torch.Tensor, *, n_seqs: int, max_q_len: int, out_dtype: torch.dtype) -> torch.Tensor:
+        """The selective scan over every request's portion: with ``step = softplus(dt + dt_bias)`` per channel,
+        ``S[c, n] <- exp(step_c A[c, n]) S[c, n] + step_c x_c B_n``, ``y_c = sum_n S[c, n] C_n + D_c x_c``, result
+        ``y * silu(z)``.  ``x``, ``dt``, ``z``: ``[T, channels]``; ``B``, ``C``: ``[T, n]`` (all of one dtype; column ranges of
+        wider rows will do); ``A`` float32 ``[channels, n]``, ``D`` and ``dt_bias`` float32 ``[channels]``; ``state`` float32
+        ``[slots, channels, n]``: read (zeros where ``fresh``) and left as the portion's last token leaves it.  All
+        arithmetic is float32."""
+        ldx, lddt, ldb, ldc, ldz = (self._rows_view(t, name) for t, name in
+                                    ((x, "scan input"), (dt, "step sizes"), (B, "B"), (C, "C"), (z, "scan gate")))
+        T, ch = x.shape
+        n = B.shape[1]
+        _need(dt.shape == (T, ch) and z.shape == (T, ch) and B.shape == (T, n) and C.shape == (T, n), "selective_scan: sizes")
+        _need(x.dtype == dt.dtype == B.dtype == C.dtype == z.dtype, "selective_scan: inputs of one dtype")
+        _need(out_dtype in _DT and (out_dtype == x.dtype or x.dtype == torch.float32), "selective_scan cannot widen bfloat16 input")
+        for t, name, shape in ((A, "A", (ch, n)), (D, "D", (ch,)), (dt_bias, "dt_bias", (ch,))):
+            _cuda_contig(t, name, torch.float32)
+            _need(tuple(t.shape) == shape, f"selective_scan: {name} must be {shape}")
+        _need(state.dim() == 3 and state.shape[1:] == (ch, n), "state must be [slots, channels, n]")
+        _need(n <= 512, f"selective_scan keeps a channel's state in registers: {n} numbers exceed 512")
+        pitch = self._state_view(state, ch * n, "scan state")
+        self._seq_index(q_start, state_slot, fresh, n_seqs)
+        out = torch.empty((T, ch), dtype=out_dtype, device=x.device)
+        rc = self._lib("selective_scan").tl_selective_scan(
+            _ptr(x), ldx, _ptr(dt), lddt, _ptr(B), ldb, _ptr(C), ldc, _ptr(z), ldz, _DT[x.dtype], _ptr(A), _ptr(D), _ptr(dt_bias),
+            _ptr(state), pitch, _ptr(q_start), _ptr(state_slot), _ptr(fresh), _ptr(out), _DT[out_dtype], T, n_seqs, ch, n, _stream())
+        _check(rc, "selective_scan")
         self.launches += 1
         return out
 
     # ------------------------------------------- activations by name, depth average, map combination
-    _ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2}
+    _ACTS = {"silu": 0, "gelu_tanh": 1, "relu2": 2, "clamped_swish": 3}      # (the last one: gated forms of the experts' kernels only)
 
     @_timed
     def depth_mix(self, history: torch.Tensor, coef: torch.Tensor, n: int, out: torch.Tensor,
@@ -570,7 +704,7 @@ class NativeOps:
     def rope_store(self, proj: torch.Tensor, positions: torch.Tensor, table: torch.Tensor, *, n_q_heads: int, n_k_heads: int,
                    n_v_heads: int, head_dim: int, v_head_dim: int, rot_dims: int, interleaved: bool, n_extra: int,
                    k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], slot_mapping: Optional[torch.Tensor],
-                   page_size: int, out_dtype: torch.dtype):
+                   page_size: int, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None):
         """What follows a stacked projection ``[q heads | k heads | v heads | extra]`` (``[T, width]`` or
         float32 partial sums): the first ``rot_dims`` coordinates of every q and k head are rotated by
         the position's angles (``table`` float32 ``[positions, rot_dims / 2, 2]``), k goes to
@@ -591,6 +725,9 @@ class NativeOps:
               "rotary table must be [positions, rot_dims / 2, 2]")
         T = proj.shape[-2]
         _need(positions.numel() == T, "one position per token")
+        if bias is not None:          # float32 [width], added to the row before anything else
+            _cuda_contig(bias, "bias", torch.float32)
+            _need(bias.numel() == width, "one bias per column of the projection")
         if n_k_heads:
             _cuda_contig(k_pages, "k_pages", out_dtype)
             _cuda_contig(v_pages, "v_pages", out_dtype)
@@ -605,7 +742,7 @@ class NativeOps:
         q = torch.empty((T, n_q_heads, head_dim), dtype=out_dtype, device=proj.device)
         extra = torch.empty((T, n_extra), dtype=out_dtype, device=proj.device) if n_extra else None
         rc = self._lib("rope").tl_rope_store(
-            _ptr(proj), _DT[proj.dtype], splits, _ptr(positions), _ptr(table), _ptr(slot_mapping if k_pages is not None else None),
+            _ptr(proj), _DT[proj.dtype], splits, _ptr(bias), _ptr(positions), _ptr(table), _ptr(slot_mapping if k_pages is not None else None),
             _ptr(q), _ptr(extra), _ptr(k_pages), _ptr(v_pages), _DT[out_dtype], T, n_q_heads, n_k_heads, n_v_heads, head_dim,
             v_head_dim, rot_dims, n_extra, page_size, table.shape[0], 1 if interleaved else 0, _stream())
         _check(rc, "rope_store")
@@ -672,7 +809,7 @@ class NativeOps:
     @_timed
     def short_conv(self, x: torch.Tensor, w: torch.Tensor, state: Optional[torch.Tensor], q_start: torch.Tensor,
                    state_slot: torch.Tensor, fresh: torch.Tensor, *, n_seqs: int, max_q_len: int, activation: Optional[str],
-                   residual: bool, out_dtype: torch.dtype) -> torch.Tensor:
+                   residual: bool, out_dtype: torch.dtype, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Causal convolution over time on every channel: ``out_t = sum_j w[:, j] x_(t - taps + 1 + j)`` (plus ``x_t``
         with ``residual``), then ``silu`` if asked for.  ``x`` is ``[T, C]`` (a column range of a wider row will do),
         ``w`` float32 ``[C, taps]``; ``state`` (float32 ``[slots, taps - 1, C]``, ``None`` with one tap) holds every
@@ -682,6 +819,9 @@ class NativeOps:
         C, taps = w.shape
         _need(x.shape[1] == C and 1 <= taps <= 8, "short_conv: x [T, C] against w [C, taps], at most 8 taps")
         _need(activation in (None, "silu"), f"short_conv knows no activation {activation!r}")
+        if bias is not None:          # float32 [C], added to the sum before the activation
+            _cuda_contig(bias, "convolution bias", torch.float32)
+            _need(bias.numel() == C, "one bias per channel")
         _need(out_dtype in _DT and (out_dtype == x.dtype or x.dtype == torch.float32), "short_conv cannot widen bfloat16 input")
         self._seq_index(q_start, state_slot, fresh, n_seqs)
         pitch = ctypes.c_longlong(0)
@@ -691,7 +831,7 @@ class NativeOps:
         T = x.shape[0]
         out = torch.empty((T, C), dtype=out_dtype, device=x.device)
         rc = self._lib("matrix_state").tl_short_conv(
-            _ptr(x), _DT[x.dtype], ldx, _ptr(w), _ptr(state if taps > 1 else None), pitch, _ptr(q_start), _ptr(state_slot),
+            _ptr(x), _DT[x.dtype], ldx, _ptr(w), _ptr(bias), _ptr(state if taps > 1 else None), pitch, _ptr(q_start), _ptr(state_slot),
             _ptr(fresh), _ptr(out), _DT[out_dtype], T, n_seqs, C, taps, max_q_len, 1 if activation == "silu" else 0,
             1 if residual else 0, _stream())
         _check(rc, "short_conv")
@@ -882,15 +1022,23 @@ class NativeOps:
     # ----------------------------------------------------------------- experts
     @_timed
     def moe_route(self, x: torch.Tensor, w_router: torch.Tensor, correction: Optional[torch.Tensor], *, n_experts: int,
-                  top: int, scale: float, renormalize: bool, shared_gate: bool, logit_bias: Optional[torch.Tensor] = None):
+                  top: int, scale: float, renormalize: bool, shared_gate: bool, logit_bias: Optional[torch.Tensor] = None,
+                  score: str = "softmax", n_groups: int = 1, keep_groups: int = 1, group_score_top: int = 2,
+                  renorm_eps: float = 0.0):
         """Router of a layer of experts: ``s = softmax(w_router[:E] x)`` in float32, the ``top`` experts
         with the largest ``s + correction`` chosen, weights ``s * scale`` (over their sum with
         ``renormalize``); with ``shared_gate`` the row ``w_router[E]`` gives ``sigmoid(.)`` per token.  ``logit_bias``
         (float32 ``[E]``) is added to the logits first.  (With ``renormalize`` and a scale of one the weights are
-        the softmax over the chosen logits alone.)
+        the softmax over the chosen logits alone.)  ``score="sigmoid"``: ``s = sigmoid(z)``, each expert by itself.
+        ``n_groups > 1``: the experts form so many equal groups of neighbours, a group's score is the sum of its
+        ``group_score_top`` largest ``s + correction``, and only experts of the ``keep_groups`` best groups can be chosen.
+        ``renorm_eps`` is added to the sum that ``renormalize`` divides by.
         Returns ``(chosen int32 [T, top], weights float32 [T, top], gate float32 [T] or None)``."""
         _cuda_contig(x, "router input")
         _cuda_contig(w_router, "router weight", torch.float32)
+        _need(score in ("softmax", "sigmoid"), f"a router's scores are 'softmax' or 'sigmoid', got {score!r}")
+        _need(n_groups >= 1 and n_experts % n_groups == 0 and 0 < keep_groups <= n_groups and group_score_top >= 1
+              and keep_groups * (n_experts // n_groups) >= top, "the kept groups must hold at least `top` experts")
         _need(x.dim() == 2 and x.dtype in _DT and w_router.dim() == 2 and w_router.shape[1] == x.shape[1]
               and w_router.shape[0] == n_experts + (1 if shared_gate else 0), "router: x [T, dim] against w [E (+ 1), dim]")
         if correction is not None:
@@ -920,7 +1068,8 @@ class NativeOps:
         weights = torch.empty((T, top), dtype=torch.float32, device=x.device)
         gate = torch.empty((T,), dtype=torch.float32, device=x.device) if shared_gate else None
         rc = lib.tl_moe_select(_ptr(logits), _ptr(correction), _ptr(logit_bias), _ptr(chosen), _ptr(weights), _ptr(gate), T, n_experts, top,
-                               ctypes.c_float(scale), 1 if renormalize else 0, _stream())
+                               ctypes.c_float(scale), 1 if renormalize else 0, 1 if score == "sigmoid" else 0, n_groups, keep_groups,
+                               group_score_top, ctypes.c_float(renorm_eps), _stream())
         _check(rc, "moe_select")
         self.launches += 1
         return chosen, weights, gate
@@ -930,11 +1079,12 @@ class NativeOps:
     @_timed
     def moe_experts(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, w_up: torch.Tensor,
                     w_down: torch.Tensor, *, activation: str, shared: Optional[torch.Tensor] = None,
-                    shared_gate: Optional[torch.Tensor] = None, gated: bool = False) -> torch.Tensor:
+                    shared_gate: Optional[torch.Tensor] = None, gated: bool = False, act_params=None) -> torch.Tensor:
         """``out[t] = sum_k weights[t, k] * down_e(act(up_e x[t]))`` with ``e = chosen[t, k]``, plus
         ``shared[t]`` (``[T, dim]`` or float32 partial sums) times ``shared_gate[t]`` where given.
         With ``gated`` an expert is ``down_e(act(gate_e x) * up_e x)`` and ``w_up`` is ``[E, 2 * hidden, dim]``, an expert's
-        rows being ``[gate; up]``.
+        rows being ``[gate; up]``; ``activation="clamped_swish"`` (gated only) with ``act_params = (limit, alpha, up_offset)``
+        is ``g * sigmoid(alpha g) * (u + up_offset)``, ``g = min(gate, limit)``, ``u = clamp(up, +-limit)``.
         ``w_up`` is ``[E, hidden, dim]``; ``w_down`` is ``[dim, >= E * hidden]``, expert ``e``'s matrix being
         the columns ``e * hidden .. (e + 1) * hidden`` (the layout in which all experts are one
         matrix too).  The (token, choice) pairs are sorted by expert on the device and both products
@@ -946,6 +1096,10 @@ class NativeOps:
         _cuda_contig(w_up, "experts' up weights", x.dtype)
         _cuda_contig(w_down, "experts' down weights", x.dtype)
         _need(activation in self._ACTS, f"unknown activation {activation!r}")
+        clamped = activation == "clamped_swish"
+        _need(not clamped or (gated and act_params is not None and len(act_params) == 3), "the clamped activation goes with gated experts and (limit, alpha, up_offset)")
+        gate_fn = (lambda t: self.glu(t, limit=act_params[0], alpha=act_params[1], up_offset=act_params[2])) if clamped \
+            else (lambda t: self.gated_act(t, activation))
         _need(x.dim() == 2 and x.dtype in _DT and chosen.dim() == 2 and chosen.shape == weights.shape and chosen.shape[0] == x.shape[0],
               "experts: x [T, dim], chosen and weights [T, top]")
         T, dim = x.shape
@@ -971,7 +1125,7 @@ class NativeOps:
             _check(lib.tl_moe_gather(_ptr(x), _DT[x.dtype], _ptr(order), _ptr(xs), pairs, dim, top, _stream()), "moe_gather")
             self.launches += 1
             u = grouped(xs, w_up.transpose(1, 2), offs=ends, out_dtype=x.dtype)
-            u = self.gated_act(u, activation) if gated else self.activation(u, activation)
+            u = gate_fn(u) if gated else self.activation(u, activation)
             y = grouped(u, w_down.as_strided((E, hidden, dim), (hidden, 1, ldd)), offs=ends, out_dtype=x.dtype)
         else:
             u = torch.empty((pairs, up_rows), dtype=x.dtype, device=x.device)
@@ -979,7 +1133,7 @@ class NativeOps:
                                    -1 if gated else self._ACTS[activation], ctypes.c_longlong(up_rows * dim), ctypes.c_longlong(dim),
                                    _stream()), "moe_gemm (up)")
             if gated:
-                u = self.gated_act(u, activation)
+                u = gate_fn(u)
             y = torch.empty((pairs, dim), dtype=x.dtype, device=x.device)
             _check(lib.tl_moe_gemm(_ptr(u), _ptr(w_down), _ptr(y), _DT[x.dtype], _ptr(tiles), _ptr(order), 0, pairs, E, dim, hidden,
                                    -1, ctypes.c_longlong(hidden), ctypes.c_longlong(ldd), _stream()), "moe_gemm (down)")
@@ -1012,13 +1166,16 @@ class NativeOps:
 
     @_timed
     def moe_dense_hidden(self, x: torch.Tensor, chosen: torch.Tensor, weights: torch.Tensor, gate: Optional[torch.Tensor],
-                         w_up_all: torch.Tensor, *, n_experts: int, hidden: int, activation: str, gated: bool = False) -> torch.Tensor:
+                         w_up_all: torch.Tensor, *, n_experts: int, hidden: int, activation: str, gated: bool = False,
+                         act_params=None, extra_act_params=None) -> torch.Tensor:
         """The hidden rows of *all* experts for a few tokens: ``w_up_all`` is every expert's up matrix
         stacked (``[E * hidden + extra, dim]``, the ``extra`` rows a shared expert's); returns
         ``[T, E * hidden + extra]`` with ``act(up_e x[t]) * weight(t, e)`` in expert ``e``'s columns (zero
         where the token did not choose it) and ``act(.) * gate[t]`` in the extra ones.  With ``gated`` an expert's rows
-        of ``w_up_all`` are ``[gate; up]`` (``2 * hidden``, no extra rows) and its ``hidden`` columns of the result hold
-        ``act(gate_e x) * (up_e x) * weight``.  The product of
+        of ``w_up_all`` are ``[gate; up]`` (``2 * hidden``) and its ``hidden`` columns of the result hold
+        ``act(gate_e x) * (up_e x) * weight``; extra rows are then a shared expert's ``[gate; up]`` too.  With
+        ``activation="clamped_swish"`` (gated only) ``act_params`` and ``extra_act_params`` are ``(limit, alpha, up_offset)`` of
+        the experts and of the shared expert.  The product of
         that with the experts' down matrices side by side (``[dim, E * hidden + extra]``) is the layer's
         output."""
         _cuda_contig(chosen, "chosen", torch.int32)
@@ -1027,7 +1184,12 @@ class NativeOps:
         T, top = chosen.shape
         width = w_up_all.shape[0] // (2 if gated else 1)
         extra = width - n_experts * hidden
-        _need((not gated or extra == 0) and extra >= 0 and x.shape[0] == T and weights.shape == chosen.shape, "moe_dense_hidden: shapes disagree")
+        clamped = activation == "clamped_swish"
+        _need(not clamped or (gated and act_params is not None), "the clamped activation goes with gated experts and (limit, alpha, up_offset)")
+        _need((not gated or extra == 0 or clamped) and extra >= 0 and x.shape[0] == T and weights.shape == chosen.shape,
+              "moe_dense_hidden: shapes disagree")
+        limit, alpha, up_offset = act_params if clamped else (0.0, 0.0, 0.0)
+        extra_limit = (extra_act_params or act_params)[0] if clamped else 0.0
         if gate is not None:
             _cuda_contig(gate, "shared gate", torch.float32)
         u = self.linear(x, w_up_all, partials_ok=True)
@@ -1035,7 +1197,8 @@ class NativeOps:
         out = torch.empty((T, width), dtype=x.dtype, device=x.device)
         rc = self._lib("moe").tl_moe_scale_act(_ptr(u), _DT[u.dtype], splits, ctypes.c_longlong(u.stride(0) if splits > 1 else 0),
                                               _ptr(chosen), _ptr(weights), _ptr(gate), _ptr(out), _DT[x.dtype], T, n_experts, hidden,
-                                              extra, top, self._ACTS[activation], 1 if gated else 0, _stream())
+                                              extra, top, self._ACTS[activation], 1 if gated else 0, ctypes.c_float(limit),
+                                              ctypes.c_float(alpha), ctypes.c_float(up_offset), ctypes.c_float(extra_limit), _stream())
         _check(rc, "moe_scale_act")
         self.launches += 1
         return out
@@ -1312,7 +1475,8 @@ class NativeOps:
                         out: Optional[torch.Tensor] = None, keep_first: int = 0,
                         distance_bias: Optional[torch.Tensor] = None, distance_buckets: Optional[torch.Tensor] = None,
                         gate: Optional[torch.Tensor] = None, n_v_heads: Optional[int] = None,
-                        out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                        out_dtype: Optional[torch.dtype] = None, softcap: float = 0.0, sinks: Optional[torch.Tensor] = None,
+                        value_dim: Optional[int] = None) -> torch.Tensor:
         """``impl``: ``"general"`` (CUDA cores, any supported size, both dtypes), ``"mma"`` (tensor
         cores, bfloat16, head_dim 16/32/64/128), ``"decode"`` (tensor cores fed by TMA, bfloat16,
         head_dim 64/128, steps whose requests bring one token or very few), ``"prefill"``
@@ -1334,13 +1498,18 @@ class NativeOps:
         ``[T, H * v_dim]``, in q's dtype), by which the result is multiplied; ``n_v_heads`` (``v_pages`` has
         fewer heads than ``k_pages``: key head ``j`` goes with value head ``j % n_v_heads``, several maps
         with keys of their own over one set of values) and ``out_dtype=torch.float32`` (the result
-        leaves unrounded whatever q's dtype)."""
+        leaves unrounded whatever q's dtype); ``softcap = c > 0`` (the scaled score ``s`` becomes ``c * tanh(s / c)``),
+        ``sinks`` (float32 ``[H]``: ``exp(sinks[h])`` joins the softmax's denominator, a key without a value that is neither
+        scaled nor capped) and ``value_dim`` (``v_pages`` is ``k_pages`` and a value is the first ``value_dim`` coordinates
+        of a stored key; the result is ``[T, H, value_dim]``)."""
         if keep_first or distance_bias is not None or gate is not None or v_pages.shape[-1] != q.shape[-1] \
-                or q.shape[-1] % 16 != 0 or v_pages.shape[1] != k_pages.shape[1] or out_dtype not in (None, q.dtype):
+                or q.shape[-1] % 16 != 0 or v_pages.shape[1] != k_pages.shape[1] or out_dtype not in (None, q.dtype) \
+                or softcap or sinks is not None or value_dim:
             _need(impl in ("auto", "general", "mma"), "only the general and the mma.sync attention kernels take these options")
             return self._paged_attention_general(q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len,
                                                  max_kv_len, scale, window, page_size, allow_split, n_tokens, out,
-                                                 keep_first, distance_bias, distance_buckets, gate, impl, n_v_heads, out_dtype)
+                                                 keep_first, distance_bias, distance_buckets, gate, impl, n_v_heads, out_dtype,
+                                                 softcap, sinks, value_dim)
         _cuda_contig(q, "q")
         _cuda_contig(k_pages, "k_pages", q.dtype)
         _cuda_contig(v_pages, "v_pages", q.dtype)
@@ -1431,12 +1600,14 @@ class NativeOps:
     class _AttentionOptions(ctypes.Structure):
         _fields_ = [("v_head_dim", ctypes.c_int), ("keep_first", ctypes.c_int), ("rel", ctypes.c_void_p),
                     ("bucket", ctypes.c_void_p), ("n_bucket", ctypes.c_int), ("gate", ctypes.c_void_p),
-                    ("gate_mode", ctypes.c_int), ("n_v_heads", ctypes.c_int), ("out_f32", ctypes.c_int)]
+                    ("gate_mode", ctypes.c_int), ("n_v_heads", ctypes.c_int), ("out_f32", ctypes.c_int),
+                    ("softcap", ctypes.c_float), ("sinks", ctypes.c_void_p), ("v_stride", ctypes.c_int)]
 
     def _paged_attention_general(self, q, k_pages, v_pages, block_table, q_start, kv_len, n_seqs, max_q_len, max_kv_len,
                                  scale, window, page_size, allow_split, n_tokens, out, keep_first, distance_bias,
                                  distance_buckets, gate, impl: str = "general", n_v_heads: Optional[int] = None,
-                                 out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+                                 out_dtype: Optional[torch.dtype] = None, softcap: float = 0.0,
+                                 sinks: Optional[torch.Tensor] = None, value_dim: Optional[int] = None) -> torch.Tensor:
         """The CUDA-core kernel with everything it can do (see :meth:`paged_attention`), or, with
         ``impl`` "auto" or "mma", in bfloat16 and for sizes it takes (keys and values multiples of 8
         up to 128), the extended form of the mma.sync kernel, which does the same."""
@@ -1451,6 +1622,11 @@ class NativeOps:
         T = T_all if n_tokens is None else int(n_tokens)
         _need(0 < T <= T_all, "n_tokens must lie within q")
         n_kv_heads, v_dim = k_pages.shape[1], v_pages.shape[3]
+        v_stride = 0
+        if value_dim:
+            _need(v_pages.data_ptr() == k_pages.data_ptr() and 0 < value_dim <= head_dim,
+                  "value_dim: values are the first coordinates of the stored keys (v_pages is k_pages)")
+            v_dim, v_stride = int(value_dim), head_dim
         self.check_attention_sizes(n_heads, n_kv_heads, head_dim, q.dtype, v_dim)
         v_heads = v_pages.shape[1]
         _need(n_v_heads in (None, v_heads) and n_kv_heads % v_heads == 0, "n_v_heads must be the heads of v_pages and divide the key heads")
@@ -1469,7 +1645,13 @@ class NativeOps:
             _cuda_contig(out, "out", out_dtype)
             _need(out.shape == (T_all, n_heads, v_dim), "out must be [tokens, heads, v_dim]")
         opt = self._AttentionOptions(v_dim, int(keep_first), None, None, 0, None, 0, v_heads,
-                                     1 if (out_dtype == torch.float32 and q.dtype != torch.float32) else 0)
+                                     1 if (out_dtype == torch.float32 and q.dtype != torch.float32) else 0,
+                                     float(softcap or 0.0), None, v_stride)
+        _need(opt.softcap >= 0.0, "softcap must not be negative")
+        if sinks is not None:
+            _cuda_contig(sinks, "sinks", torch.float32)
+            _need(sinks.numel() == n_heads, "one sink per query head")
+            opt.sinks = sinks.data_ptr()
         if distance_bias is not None:
             _cuda_contig(distance_bias, "distance_bias", torch.float32)
             _cuda_contig(distance_buckets, "distance_buckets", torch.int32)
@@ -1485,7 +1667,8 @@ class NativeOps:
         n_splits, floats = ctypes.c_int(0), ctypes.c_longlong(0)
         mma_ok = (q.dtype == torch.bfloat16 and impl in ("auto", "mma") and self.use_mma_options
                   and self._lib("attention_mma").tl_attention_mma_ex_supports(head_dim, v_dim) == 1
-                  and (v_pages.data_ptr() != k_pages.data_ptr() or v_dim == head_dim))
+                  and (v_pages.data_ptr() != k_pages.data_ptr() or v_dim == head_dim)
+                  and not softcap and sinks is None and not v_stride)
         _need(impl != "mma" or mma_ok, "the mma.sync kernel takes bfloat16 and keys and values that are multiples of 8 up to 128")
         if mma_ok:
             lib = self._lib("attention_mma")
