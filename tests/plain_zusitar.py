@@ -147,8 +147,10 @@ def bounded_expert(h, W, p: str, limit: float, rounding) -> torch.Tensor:
     return _r(y @ W[p + ".down"].T, rounding)
 
 
-def route(z: torch.Tensor, router: Mapping) -> (torch.Tensor, torch.Tensor):
-    """``z [n, E]`` logits -> ``(chosen [n, top], weights [n, top])``."""
+def route(z: torch.Tensor, router: Mapping, margins_out: Optional[list] = None):
+    """``z [n, E]`` logits -> ``(chosen [n, top], weights [n, top])``.  ``margins_out`` receives, per token, how far
+    the choice was from another one: the gap between the last group kept and the first one left out, and between
+    the last expert chosen and the first one left out among those that could be chosen."""
     E, top = router["experts"], router["top"]
     groups = router.get("groups") or {"count": 1, "keep": 1}
     s = torch.sigmoid(z)
@@ -160,18 +162,25 @@ def route(z: torch.Tensor, router: Mapping) -> (torch.Tensor, torch.Tensor):
         best = score.topk(groups["keep"], dim=-1).indices
         keep = torch.zeros_like(score, dtype=torch.bool).scatter_(1, best, True)
         allowed = keep[:, :, None].expand(-1, -1, per).reshape(s.shape)
-    chosen = s.masked_fill(~allowed, float("-inf")).topk(top, dim=-1).indices
+        if margins_out is not None and groups["keep"] < groups["count"]:
+            ordered = score.sort(-1, descending=True).values
+            margins_out.append(ordered[:, groups["keep"] - 1] - ordered[:, groups["keep"]])
+    open_scores = s.masked_fill(~allowed, float("-inf"))
+    if margins_out is not None and top < int(allowed[0].sum()):
+        ordered = open_scores.sort(-1, descending=True).values
+        margins_out.append(ordered[:, top - 1] - ordered[:, top])
+    chosen = open_scores.topk(top, dim=-1).indices
     w = s.gather(1, chosen)
     w = w / (w.sum(-1, keepdim=True) + 1e-20) * router["scale"]
     return chosen, w
 
 
-def experts_ffn(h, W, p: str, mlp: Mapping, rounding) -> torch.Tensor:
+def experts_ffn(h, W, p: str, mlp: Mapping, rounding, margins_out: Optional[list] = None) -> torch.Tensor:
     n = h.shape[0]
     router = mlp["router"]
     hr = h if rounding is None else h.to(rounding).to(F64)
     z = hr @ W[p + ".router"].T
-    chosen, w = route(z, router)
+    chosen, w = route(z, router, margins_out)
     out = torch.zeros(n, h.shape[1], dtype=F64)
     for e in range(router["experts"]):
         rows, slot = (chosen == e).nonzero(as_tuple=True)
@@ -194,8 +203,10 @@ def run_order(config: Mapping) -> List[tuple]:
     return runs + [(i, None) for i in range(loop["stop"], n)]
 
 
-def forward(config: Mapping, W: Mapping[str, torch.Tensor], tokens, rounding=None, layers_out: Optional[list] = None) -> torch.Tensor:
-    """Logits ``[n, vocab]`` (float64) of one whole sequence."""
+def forward(config: Mapping, W: Mapping[str, torch.Tensor], tokens, rounding=None, layers_out: Optional[list] = None,
+            margins_out: Optional[list] = None, mixer_hook=None) -> torch.Tensor:
+    """Logits ``[n, vocab]`` (float64) of one whole sequence.  ``layers_out`` receives the stream after every layer
+    run, ``margins_out`` the routers' margins (see :func:`route`); ``mixer_hook(run, y)`` may replace a mixer's result."""
     W = {k: v.to(F64) for k, v in W.items()}
     eps = config["norm"]["eps"]
     x0 = W["embed"][torch.as_tensor(tokens, dtype=torch.long)] * config["embedding"]["scale"]
@@ -218,7 +229,8 @@ def forward(config: Mapping, W: Mapping[str, torch.Tensor], tokens, rounding=Non
         mlp = layer.get("mlp")
         if mlp is not None:
             h = _r(rms(x, eps) * W[p + ".norm2"], rounding)
-            y = dense_ffn(h, W, p + ".mlp", rounding) if mlp["kind"] == "dense" else experts_ffn(h, W, p + ".mlp", mlp, rounding)
+            y = dense_ffn(h, W, p + ".mlp", rounding) if mlp["kind"] == "dense" \
+                else experts_ffn(h, W, p + ".mlp", mlp, rounding, margins_out)
             x = x + rms(y, eps) * W[p + ".norm2b"]
         if layers_out is not None:
             layers_out.append(x.clone())
