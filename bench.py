@@ -336,9 +336,35 @@ def _nunosun_config(z, vocab, max_len):
                          tuple(LayerConfig(*kinds[i % 2]) for i in range(z["layers"])), max_seq_len=max_len)
 
 
+# Zusitar at the same widths: a selective-scan layer with a dense feed-forward, latent attention (queries through a
+# latent, a rotated key part shared by the heads) with grouped experts, a selective-scan layer with experts, and
+# attention with capped scores, sinks and a gate per head, with experts; every layer runs once
+ZUSITAR_SIZES = {
+    "w2048": dict(RAKUVIK_SIZES["w2048"], scan_state=16, conv=4, q_rank=768, kv_rank=96, latent_dim=96, latent_rot=32, groups=4, keep_groups=2),
+    "w4096": dict(RAKUVIK_SIZES["w4096"], scan_state=16, conv=4, q_rank=1536, kv_rank=96, latent_dim=96, latent_rot=32, groups=4, keep_groups=2),
+}
+
+
+def _zusitar_config(z, vocab, max_len):
+    from torchllms_b200.models.zusitar import AttentionConfig, LatentConfig, LayerConfig, MlpConfig, ScanConfig, ZusitarConfig
+    hd = z["head_dim"]
+    scan = ScanConfig(inner=2 * z["dim"], state=z["scan_state"], dt_rank=z["dim"] // 16, conv=z["conv"])
+    latent = LatentConfig(heads=z["heads"], dim=z["latent_dim"], rot_dim=z["latent_rot"], vdim=hd, q_rank=z["q_rank"], kv_rank=z["kv_rank"],
+                          scale=(z["latent_dim"] + z["latent_rot"]) ** -0.5, rot_dims=z["latent_rot"], rot_base=500000.0)
+    att = AttentionConfig(heads=z["heads"], kv_heads=z["kv_heads"], dim=hd, vdim=hd, scale=hd ** -0.5, softcap=30.0, rot_dims=z["rot_dims"],
+                          rot_base=250000.0)
+    dense = MlpConfig("dense", z["ff"])
+    moe = MlpConfig("moe", z["expert_ff"], limit=7.0, experts=z["experts"], top=z["top"], router_scale=2.0, groups=z["groups"],
+                    keep_groups=z["keep_groups"], shared_ff=z["shared_ff"], shared_limit=7.0)
+    kinds = [(scan, dense), (latent, moe), (scan, moe), (att, moe)]
+    return ZusitarConfig("Zusitar", vocab, z["dim"], 1e-6, 1.0, tuple(LayerConfig(*kinds[i % 4]) for i in range(z["layers"])),
+                         max_seq_len=max_len)
+
+
 # design -> (its name, the table of sizes, how its configuration is made, the model it stands beside)
 DESIGNS = {"nagolix": ("Nagolix", DESIGN_SIZES, _nagolix_config, "llama"), "rakuvik": ("Rakuvik", RAKUVIK_SIZES, _rakuvik_config, "llama"),
-           "nunosun": ("Nunosun", NUNOSUN_SIZES, _nunosun_config, "rakuvik")}
+           "nunosun": ("Nunosun", NUNOSUN_SIZES, _nunosun_config, "rakuvik"),
+           "zusitar": ("Zusitar", ZUSITAR_SIZES, _zusitar_config, "rakuvik")}
 
 
 def design_workload(args, peaks, design="nagolix"):
@@ -348,7 +374,7 @@ def design_workload(args, peaks, design="nagolix"):
     model's time goes (per kernel-library call, from ``ops.profile()``).  Nagolix layers alternate latent
     attention, attention, latent attention reading the first one's latents, attention; Rakuvik layers
     alternate minGRU with a dense feed-forward, differential attention with experts, minGRU with experts,
-    differential attention reading the first one's keys and values with experts.  Nunosun stands beside
+    differential attention reading the first one's keys and values with experts.  Nunosun and Zusitar stand beside
     Rakuvik, the closest model (recurrent layers, attention, experts), at the same sizes."""
     import torch
     from torchllms_b200.engine.step import StepEntry
@@ -446,10 +472,10 @@ def main():
     ap.add_argument("--layers", type=int, default=SHAPE_8B["n_layers"], help="fewer layers than the shape has (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="only the headline batch and the prefill")
-    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix", "design_rakuvik", "design_nunosun"] + sorted(SERVE),
+    ap.add_argument("--workload", default="decode_8b", choices=["decode_8b", "design_nagolix", "design_rakuvik", "design_nunosun", "design_zusitar"] + sorted(SERVE),
                     help="decode_8b: the headline (default); serve_1b, long_3b: whole serving runs through LLM.generate; "
                          "design_nagolix, design_rakuvik: that design beside the Llama decoder at equal sizes; "
-                         "design_nunosun: Nunosun beside Rakuvik at equal sizes")
+                         "design_nunosun, design_zusitar: that design beside Rakuvik at equal sizes")
     ap.add_argument("--context-len", type=int, default=PROMPT_LEN,
                     help="prompt length of the decode measurements (the headline is 2,048; the prefill figure stays at 2,048)")
     ap.add_argument("--long-contexts", type=lambda t: [int(x) for x in t.split(",") if x], default=[8192, 32768],

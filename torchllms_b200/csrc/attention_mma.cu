@@ -21,8 +21,9 @@
 // instantiated size, the tiles' spare columns zero-filled), one stored vector read as key and as
 // value (the value tile is the key tile), a window that keeps a request's first keys visible (they
 // are walked as tiles of their own ahead of the window's), a bias by bucketed distance added to the
-// scaled score, and an output gate per head or per element; and it multiplies probabilities as three
-// bfloat16 terms, which add up to the float32 probability exactly.
+// scaled score, an output gate per head or per element, a cap on the scaled score (c * tanh(s / c)), a learned
+// sink per head in the softmax's denominator, and values that are the first coordinates of the stored keys; and
+// it multiplies probabilities as three bfloat16 terms, which add up to the float32 probability exactly.
 #include "common.cuh"
 #include <limits.h>
 #include <math.h>
@@ -67,6 +68,9 @@ struct MmaParams {
     int bias_cols;              // row split: the bias of so many distances (from 0) is tabulated in shared memory per head of the tile
     int n_v_heads;              // value heads of v_pages; key head j goes with value head j % n_v_heads
     int out_f32;                // 1: out holds float32
+    float cap_log2;             // softcap * log2(e); 0: scores are not capped
+    float scale_over_cap;       // scale / softcap
+    const float* sinks;         // [n_heads] or null (natural-log scale, as stored)
 };
 
 __device__ __forceinline__ unsigned smem_addr(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -280,7 +284,15 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             float mx[2] = {-INFINITY, -INFINITY};
             const int share_lo = k0 + key_off, share_hi = share_lo + 16 * KG;   // this warp's keys of the tile
             const bool biased = EXT && p.rel != nullptr;
-            const float sl = biased ? 1.f : p.scale_log2;       // biased scores are put on the base-2 scale below
+            const bool capped = EXT && p.cap_log2 > 0.f;        // (never together with a bias: the host sends those elsewhere)
+            if (capped) {
+                // c * tanh(score * scale / c), on the base-2 scale; hidden keys are masked below as usual
+#pragma unroll
+                for (int nt = 0; nt < 2 * KG; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) s[nt][e] = p.cap_log2 * tanhf(s[nt][e] * p.scale_over_cap);
+            }
+            const float sl = (biased || capped) ? 1.f : p.scale_log2;       // biased and capped scores are on the base-2 scale already
             const bool all_visible = share_hi <= k_hi && share_hi - 1 <= warp_qmin &&
                                      (p.window <= 0 || share_lo > warp_qmax - p.window);
             if (biased && all_visible && warp_qmax - share_lo < bias_cols) {
@@ -428,6 +440,15 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
             const int head = kvh * p.group + g0 + rr % ng;
             const size_t row = (size_t)tok * p.n_heads + head;
             __nv_bfloat16* dst = p.out + row * dv;
+            if (EXT && p.sinks != nullptr) {
+                // one more term of the denominator, without a value: everything is rescaled to max(m, sink)
+                const float sink2 = p.sinks[head] * LOG2E;
+                const float M = fmaxf(m[i], sink2);
+                const float a = ex2(m[i] - M);
+                l[i] = l[i] * a + ex2(sink2 - M);
+#pragma unroll
+                for (int nt = 0; nt < HD / 8; ++nt) { o[nt][2 * i] *= a; o[nt][2 * i + 1] *= a; }
+            }
             float inv = l[i] > 0.f ? 1.f / l[i] : 0.f;
             if (EXT && p.gate_mode == 1) inv *= __bfloat162float(p.gate[row]);
 #pragma unroll
@@ -485,6 +506,13 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
         const size_t row = (size_t)tok * p.n_heads + head;
         if (EXT && d >= dv) continue;
         if (p.n_splits == 1) {
+            if (EXT && p.sinks != nullptr) {
+                const float sink2 = p.sinks[head] * LOG2E;
+                const float M2 = fmaxf(M, sink2);
+                const float f = exp2f(M - M2);          // M = -inf (no key seen) gives 0
+                num *= f;
+                den = den * f + exp2f(sink2 - M2);
+            }
             float v = den > 0.f ? num / den : 0.f;
             if (EXT && p.gate_mode == 1) v *= __bfloat162float(p.gate[row]);
             else if (EXT && p.gate_mode == 2) v *= __bfloat162float(p.gate[row * dv + d]);
@@ -506,7 +534,8 @@ __global__ void __launch_bounds__(NT, KEY_SPLIT ? 4 : 2) attention_mma_kernel(co
 constexpr int MERGE_MAX_SPLITS = 256;
 __global__ void merge_partials_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       __nv_bfloat16* __restrict__ out, int n_splits, int head_dim,
-                                      const __nv_bfloat16* __restrict__ gate = nullptr, int gate_mode = 0, int out_f32 = 0) {
+                                      const __nv_bfloat16* __restrict__ gate = nullptr, int gate_mode = 0, int out_f32 = 0,
+                                      const float* __restrict__ sinks = nullptr, int n_heads = 1) {
     __shared__ float wgt[MERGE_MAX_SPLITS];
     __shared__ float red[2];
     const size_t row = blockIdx.x;
@@ -515,7 +544,9 @@ __global__ void merge_partials_kernel(const float* __restrict__ part_o, const fl
         float M = -INFINITY;
         for (int i = threadIdx.x; i < n_splits; i += 32) M = fmaxf(M, ml[2 * i]);
         M = warp_max(M);
-        float den = 0.f;
+        const float sink = sinks != nullptr ? sinks[row % n_heads] : -INFINITY;
+        M = fmaxf(M, sink);
+        float den = threadIdx.x == 0 && sinks != nullptr ? __expf(sink - M) : 0.f;
         for (int i = threadIdx.x; i < n_splits; i += 32) {
             const float mi = ml[2 * i];
             const float w = (mi == -INFINITY) ? 0.f : __expf(mi - M);
@@ -661,7 +692,7 @@ extern "C" int tl_paged_attention_mma(const void* q, const void* k_pages, const 
     p.part_o = workspace;
     p.part_ml = workspace ? workspace + (size_t)n_tokens * n_heads * pl.n_splits * head_dim : nullptr;
     p.hd = p.dv = head_dim; p.shared_kv = 0; p.keep_first = 0; p.rel = nullptr; p.bucket = nullptr; p.n_bucket = 0; p.n_v_heads = n_kv_heads; p.out_f32 = 0;
-    p.gate = nullptr; p.gate_mode = 0; p.bias_cols = 0;
+    p.gate = nullptr; p.gate_mode = 0; p.bias_cols = 0; p.cap_log2 = 0.f; p.scale_over_cap = 0.f; p.sinks = nullptr;
 
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(pl.n_q_tiles * pl.n_splits, n_kv_heads * pl.n_gchunks, n_seqs);
@@ -693,6 +724,9 @@ struct TlAttentionOptions {
     int gate_mode;          // 0: none, 1: [tokens, n_heads], 2: [tokens, n_heads * v_head_dim]
     int n_v_heads;          // 0: as n_kv_heads; else it divides n_kv_heads, and v_pages has so many heads
     int out_f32;            // 1: out is float32
+    float softcap;          // c > 0: the scaled score s becomes c * tanh(s / c); not together with rel
+    const float* sinks;     // [n_heads] or null: exp(sinks[h]) joins the softmax's denominator
+    int v_stride;           // 0, or head_dim with v_pages == k_pages: a value is the first v_head_dim coordinates of a key
 };
 
 // 1 if the extended form takes keys of head_dim and values of v_head_dim elements, else 0.
@@ -709,7 +743,7 @@ extern "C" int tl_attention_mma_plan_ex(int n_tokens, int n_seqs, int n_heads, i
 }
 
 // q: [n_tokens, n_heads, head_dim]; out: [n_tokens, n_heads, v_head_dim]; v_pages may be k_pages itself
-// (then v_head_dim must equal head_dim).  bfloat16 only.
+// (then a value is the first v_head_dim coordinates of a stored key).  bfloat16 only.
 extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, const void* v_pages, void* out,
                                          const int* block_table, int table_stride, const int* q_start,
                                          const int* kv_len, float* workspace, int n_tokens, int n_seqs,
@@ -727,7 +761,9 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     if (o.keep_first < 0 || (o.keep_first > 0 && window == 0)) return TL_BAD_SIZE;
     if (o.rel != nullptr && (o.bucket == nullptr || o.n_bucket <= 0)) return TL_BAD_SIZE;
     if (o.gate_mode < 0 || o.gate_mode > 2 || (o.gate_mode != 0 && o.gate == nullptr)) return TL_BAD_SIZE;
-    if (v_pages == k_pages && dv != head_dim) return TL_BAD_SIZE;
+    if (v_pages == k_pages && dv > head_dim) return TL_BAD_SIZE;
+    if (o.v_stride != 0 && !(v_pages == k_pages && o.v_stride == head_dim)) return TL_BAD_SIZE;
+    if (o.softcap < 0.f || (o.softcap > 0.f && o.rel != nullptr)) return TL_BAD_SIZE;
     const int n_v_heads = o.n_v_heads > 0 ? o.n_v_heads : n_kv_heads;
     if (n_kv_heads % n_v_heads != 0 || (n_v_heads != n_kv_heads && v_pages == k_pages)) return TL_BAD_SIZE;
     if (!aligned16(q) || !aligned16(k_pages) || !aligned16(v_pages) || !aligned16(out)) return TL_BAD_ALIGN;
@@ -753,6 +789,9 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     p.keep_first = o.keep_first; p.rel = o.rel; p.bucket = o.bucket; p.n_bucket = o.n_bucket;
     p.gate = (const __nv_bfloat16*)o.gate; p.gate_mode = o.gate_mode;
     p.n_v_heads = n_v_heads; p.out_f32 = o.out_f32 ? 1 : 0;
+    p.cap_log2 = o.softcap > 0.f ? o.softcap * LOG2E : 0.f;
+    p.scale_over_cap = o.softcap > 0.f ? scale / o.softcap : 0.f;
+    p.sinks = o.sinks;
     // distances a row-split CTA meets inside its window (all of them when there is no window), as far as
     // 20 KB of shared memory hold them for the heads of a tile
     p.bias_cols = 0;
@@ -775,7 +814,7 @@ extern "C" int tl_paged_attention_mma_ex(const void* q, const void* k_pages, con
     if (rc != TL_OK) return rc;
     if (pl.n_splits > 1) {
         merge_partials_kernel<<<dim3((unsigned)n_tokens * (unsigned)n_heads), dim3(dv >= 128 ? 128u : 64u), 0, s>>>(
-            p.part_o, p.part_ml, p.out, pl.n_splits, dv, p.gate, p.gate_mode, p.out_f32);
+            p.part_o, p.part_ml, p.out, pl.n_splits, dv, p.gate, p.gate_mode, p.out_f32, p.sinks, n_heads);
         TL_LAUNCH_CHECK();
     }
     return TL_OK;

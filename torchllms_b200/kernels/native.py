@@ -1667,8 +1667,7 @@ class NativeOps:
         n_splits, floats = ctypes.c_int(0), ctypes.c_longlong(0)
         mma_ok = (q.dtype == torch.bfloat16 and impl in ("auto", "mma") and self.use_mma_options
                   and self._lib("attention_mma").tl_attention_mma_ex_supports(head_dim, v_dim) == 1
-                  and (v_pages.data_ptr() != k_pages.data_ptr() or v_dim == head_dim)
-                  and not softcap and sinks is None and not v_stride)
+                  and not (softcap and distance_bias is not None))
         _need(impl != "mma" or mma_ok, "the mma.sync kernel takes bfloat16 and keys and values that are multiples of 8 up to 128")
         if mma_ok:
             lib = self._lib("attention_mma")
