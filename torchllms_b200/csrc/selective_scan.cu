@@ -15,15 +15,17 @@
 // Work split: a CTA of 128 threads takes one request and 128 / L channels, L lanes sharing a channel
 // and each holding NS of its state numbers in registers (n = lane + j * L).  Tokens come in chunks of
 // 16: dt (after softplus), x, z of the CTA's channels and B, C of the chunk are staged in shared
-// memory as float32, then every token is one pass over the lane's NS numbers, a shuffle sum over the
-// L lanes, and the chunk's outputs leave together.
+// memory as float32 (through registers, the next chunk's loads in flight while this one is walked), then
+// every token is one pass over the lane's NS numbers; the sums over the L lanes are taken for the whole
+// chunk at once, and the chunk's outputs leave together.  Per state number the arithmetic is one chain of
+// multiply-adds in token order whatever the chunks, so a prompt, its portions and its decoded tokens agree
+// to the bit.
 #include "common.cuh"
 #include <math.h>
 
 namespace {
 
 constexpr int NT = 128;
-constexpr int TT = 16;       // tokens per chunk
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct ScanParams {
@@ -45,9 +47,11 @@ struct ScanParams {
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
 
-template <typename TI, typename TO, int NS, int L>
+template <typename TI, typename TO, int NS, int L, int TT>
 __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) {
-    constexpr int CH = NT / L;            // channels per CTA
+    constexpr int CH = NT / L;                          // channels per CTA
+    constexpr int CI = (TT * CH + NT - 1) / NT;         // (token, channel) items of a chunk per thread
+    constexpr int BI = (TT * NS * L + NT - 1) / NT;     // (token, state index) items of a chunk per thread, at most
     extern __shared__ __align__(16) float sm[];
     float* s_dt = sm;                     // [TT][CH]
     float* s_x = s_dt + TT * CH;          // [TT][CH]
@@ -85,51 +89,96 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
     const TI* z = reinterpret_cast<const TI*>(p.z);
     TO* out = reinterpret_cast<TO*>(p.out);
 
+    // The chunk's inputs travel global memory -> registers -> shared memory, the next chunk's loads being issued before
+    // this chunk's tokens are walked.  Item k of a thread is (token tid / CH + k * (NT / CH), channel tid % CH): always
+    // the same channel, whose step-size bias it keeps.
+    const int my_cc = tid % CH, my_ch = c0 + my_cc, my_t0 = tid / CH;
+    const bool my_live = my_ch < p.C;
+    const float my_bias = my_live ? p.dt_bias[my_ch] : 0.f;
+    TI r_dt[CI], r_x[CI], r_z[CI], r_B[BI], r_C[BI];
+    auto fetch = [&](int t0, int nt) {
+#pragma unroll
+        for (int k = 0; k < CI; ++k) {
+            const int tt = my_t0 + k * (NT / CH);
+            if (tt < nt && my_live) {
+                const size_t row = (size_t)(start + t0 + tt);
+                r_dt[k] = dt[row * p.lddt + my_ch];
+                r_x[k] = x[row * p.ldx + my_ch];
+                r_z[k] = z[row * p.ldz + my_ch];
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < BI; ++k) {
+            const int i = tid + k * NT;
+            if (i < nt * N) {
+                const int tt = i / N, n = i - tt * N;
+                const size_t row = (size_t)(start + t0 + tt);
+                r_B[k] = Bm[row * p.ldb + n];
+                r_C[k] = Cm[row * p.ldc + n];
+            }
+        }
+    };
+    auto stage = [&](int nt) {
+#pragma unroll
+        for (int k = 0; k < CI; ++k) {
+            const int tt = my_t0 + k * (NT / CH);
+            if (tt < nt) {
+                const int i = tt * CH + my_cc;
+                s_dt[i] = my_live ? softplus_f(to_float(r_dt[k]) + my_bias) : 0.f;
+                s_x[i] = my_live ? to_float(r_x[k]) : 0.f;
+                s_z[i] = my_live ? to_float(r_z[k]) : 0.f;
+            }
+        }
+#pragma unroll
+        for (int k = 0; k < BI; ++k) {
+            const int i = tid + k * NT;
+            if (i < nt * N) {
+                s_B[i] = to_float(r_B[k]);
+                s_C[i] = to_float(r_C[k]);
+            }
+        }
+    };
+
+    fetch(0, min(TT, len));
     for (int t0 = 0; t0 < len; t0 += TT) {
         const int nt = min(TT, len - t0);
-        __syncthreads();      // the chunk before has been read (and its outputs written)
-        for (int i = tid; i < nt * CH; i += NT) {
-            const int tt = i / CH, cc = i - tt * CH;
-            const int ch = c0 + cc;
-            float vdt = 0.f, vx = 0.f, vz = 0.f;
-            if (ch < p.C) {
-                const size_t row = (size_t)(start + t0 + tt);
-                vdt = softplus_f(to_float(dt[row * p.lddt + ch]) + p.dt_bias[ch]);
-                vx = to_float(x[row * p.ldx + ch]);
-                vz = to_float(z[row * p.ldz + ch]);
-            }
-            s_dt[i] = vdt; s_x[i] = vx; s_z[i] = vz;
-        }
-        for (int i = tid; i < nt * N; i += NT) {
-            const int tt = i / N, n = i - tt * N;
-            const size_t row = (size_t)(start + t0 + tt);
-            s_B[i] = to_float(Bm[row * p.ldb + n]);
-            s_C[i] = to_float(Cm[row * p.ldc + n]);
-        }
+        __syncthreads();      // the chunk before has been walked and its outputs have left shared memory
+        stage(nt);
         __syncthreads();
-        for (int tt = 0; tt < nt; ++tt) {
-            const float d = s_dt[tt * CH + cl], xv = s_x[tt * CH + cl];
-            const float dx = d * xv;
-            float acc = 0.f;
+        if (t0 + TT < len) fetch(t0 + TT, min(TT, len - t0 - TT));
+        // The only chain from token to token is one multiply-add per state number; the sums over a channel's lanes
+        // wait until the chunk's tokens are done, so that their shuffles do not stand in that chain.
+        float acc[TT];
 #pragma unroll
-            for (int j = 0; j < NS; ++j) {
-                const int n = lane + j * L;
-                if (n < N) {
-                    S[j] = fmaf(exp2f(d * A2[j]), S[j], dx * s_B[tt * N + n]);
-                    acc = fmaf(S[j], s_C[tt * N + n], acc);
+        for (int tt = 0; tt < TT; ++tt) {
+            acc[tt] = 0.f;
+            if (tt < nt) {
+                const float d = s_dt[tt * CH + cl];
+                const float dx = d * s_x[tt * CH + cl];
+#pragma unroll
+                for (int j = 0; j < NS; ++j) {
+                    const int n = lane + j * L;
+                    if (n < N) {
+                        S[j] = fmaf(exp2f(d * A2[j]), S[j], dx * s_B[tt * N + n]);
+                        acc[tt] = fmaf(S[j], s_C[tt * N + n], acc[tt]);
+                    }
                 }
             }
+        }
 #pragma unroll
-            for (int o = L / 2; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-            if (lane == 0) s_y[tt * CH + cl] = fmaf(Dc, xv, acc);
+        for (int tt = 0; tt < TT; ++tt) {
+#pragma unroll
+            for (int o = L / 2; o > 0; o >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+            if (lane == 0 && tt < nt) s_y[tt * CH + cl] = fmaf(Dc, s_x[tt * CH + cl], acc[tt]);
         }
         __syncthreads();
-        for (int i = tid; i < nt * CH; i += NT) {
-            const int tt = i / CH, cc = i - tt * CH;
-            const int ch = c0 + cc;
-            if (ch < p.C) {
+#pragma unroll
+        for (int k = 0; k < CI; ++k) {
+            const int tt = my_t0 + k * (NT / CH);
+            if (tt < nt && my_live) {
+                const int i = tt * CH + my_cc;
                 const float zv = s_z[i];
-                out[(size_t)(start + t0 + tt) * p.C + ch] = from_float<TO>(s_y[i] * (zv / (1.f + expf(-zv))));
+                out[(size_t)(start + t0 + tt) * p.C + my_ch] = from_float<TO>(s_y[i] * (zv / (1.f + expf(-zv))));
             }
         }
     }
@@ -140,28 +189,28 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
     }
 }
 
-template <typename TI, typename TO, int NS, int L>
+template <typename TI, typename TO, int NS, int L, int TT>
 int launch(const ScanParams& p, int n_seqs, cudaStream_t s) {
     constexpr int CH = NT / L;
     const size_t smem = (size_t)(4 * TT * CH + 2 * TT * p.N) * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
     const dim3 grid((p.C + CH - 1) / CH, n_seqs);
-    return (int)tl_launch(selective_scan_kernel<TI, TO, NS, L>, grid, dim3(NT), smem, s, p);
+    return (int)tl_launch(selective_scan_kernel<TI, TO, NS, L, TT>, grid, dim3(NT), smem, s, p);
 }
 
-// lanes per channel and state numbers per lane for a state of N numbers: four numbers a lane while a warp's
-// 32 lanes reach, more beyond
+// lanes per channel, state numbers per lane and tokens per chunk for a state of N numbers: four numbers a lane
+// while a warp's 32 lanes reach, more beyond (and shorter chunks, so that a chunk's inputs still fit a thread's registers)
 template <typename TI, typename TO>
 int launch_n(const ScanParams& p, int n_seqs, cudaStream_t s) {
     const int N = p.N;
-    if (N <= 4) return launch<TI, TO, 4, 1>(p, n_seqs, s);
-    if (N <= 8) return launch<TI, TO, 4, 2>(p, n_seqs, s);
-    if (N <= 16) return launch<TI, TO, 4, 4>(p, n_seqs, s);
-    if (N <= 32) return launch<TI, TO, 4, 8>(p, n_seqs, s);
-    if (N <= 64) return launch<TI, TO, 4, 16>(p, n_seqs, s);
-    if (N <= 128) return launch<TI, TO, 4, 32>(p, n_seqs, s);
-    if (N <= 256) return launch<TI, TO, 8, 32>(p, n_seqs, s);
-    if (N <= 512) return launch<TI, TO, 16, 32>(p, n_seqs, s);
+    if (N <= 4) return launch<TI, TO, 4, 1, 16>(p, n_seqs, s);
+    if (N <= 8) return launch<TI, TO, 4, 2, 16>(p, n_seqs, s);
+    if (N <= 16) return launch<TI, TO, 4, 4, 16>(p, n_seqs, s);
+    if (N <= 32) return launch<TI, TO, 4, 8, 16>(p, n_seqs, s);
+    if (N <= 64) return launch<TI, TO, 4, 16, 16>(p, n_seqs, s);
+    if (N <= 128) return launch<TI, TO, 4, 32, 16>(p, n_seqs, s);
+    if (N <= 256) return launch<TI, TO, 8, 32, 8>(p, n_seqs, s);
+    if (N <= 512) return launch<TI, TO, 16, 32, 4>(p, n_seqs, s);
     return TL_BAD_SIZE;
 }
 
