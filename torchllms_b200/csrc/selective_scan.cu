@@ -57,8 +57,9 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
     float* s_x = s_dt + TT * CH;          // [TT][CH]
     float* s_z = s_x + TT * CH;           // [TT][CH]
     float* s_y = s_z + TT * CH;           // [TT][CH]
-    float* s_B = s_y + TT * CH;           // [TT][N]
-    float* s_C = s_B + TT * p.N;          // [TT][N]
+    constexpr int NP = NS * L;            // a row of B or C in shared memory: N numbers and zeros up to NS * L
+    float* s_B = s_y + TT * CH;           // [TT][NP]
+    float* s_C = s_B + TT * NP;           // [TT][NP]
     grid_launch_dependents();
     grid_dependency_wait();
     const int b = blockIdx.y;
@@ -110,31 +111,35 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
 #pragma unroll
         for (int k = 0; k < BI; ++k) {
             const int i = tid + k * NT;
-            if (i < nt * N) {
-                const int tt = i / N, n = i - tt * N;
+            const int tt = i / NP, n = i - tt * NP;
+            if (tt < nt && n < N) {
                 const size_t row = (size_t)(start + t0 + tt);
                 r_B[k] = Bm[row * p.ldb + n];
                 r_C[k] = Cm[row * p.ldc + n];
             }
         }
     };
+    // (places without a token or a state number hold zeros: a step of size zero leaves the state as it is)
     auto stage = [&](int nt) {
 #pragma unroll
         for (int k = 0; k < CI; ++k) {
             const int tt = my_t0 + k * (NT / CH);
-            if (tt < nt) {
+            if (tt < TT) {
                 const int i = tt * CH + my_cc;
-                s_dt[i] = my_live ? softplus_f(to_float(r_dt[k]) + my_bias) : 0.f;
-                s_x[i] = my_live ? to_float(r_x[k]) : 0.f;
-                s_z[i] = my_live ? to_float(r_z[k]) : 0.f;
+                const bool ok = my_live && tt < nt;
+                s_dt[i] = ok ? softplus_f(to_float(r_dt[k]) + my_bias) : 0.f;
+                s_x[i] = ok ? to_float(r_x[k]) : 0.f;
+                s_z[i] = ok ? to_float(r_z[k]) : 0.f;
             }
         }
 #pragma unroll
         for (int k = 0; k < BI; ++k) {
             const int i = tid + k * NT;
-            if (i < nt * N) {
-                s_B[i] = to_float(r_B[k]);
-                s_C[i] = to_float(r_C[k]);
+            const int tt = i / NP, n = i - tt * NP;
+            if (tt < TT) {
+                const bool ok = tt < nt && n < N;
+                s_B[i] = ok ? to_float(r_B[k]) : 0.f;
+                s_C[i] = ok ? to_float(r_C[k]) : 0.f;
             }
         }
     };
@@ -146,30 +151,46 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
         stage(nt);
         __syncthreads();
         if (t0 + TT < len) fetch(t0 + TT, min(TT, len - t0 - TT));
-        // The only chain from token to token is one multiply-add per state number; the sums over a channel's lanes
-        // wait until the chunk's tokens are done, so that their shuffles do not stand in that chain.
-        float acc[TT];
+        if (nt == TT) {
+            // A whole chunk, without a branch: the only chain from token to token is one multiply-add per state
+            // number; decays and inputs of later tokens are worked out beside it, and the sums over a channel's
+            // lanes wait until the chunk's tokens are done, so that their shuffles do not stand in that chain.
+            float acc[TT];
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
-            acc[tt] = 0.f;
-            if (tt < nt) {
+            for (int tt = 0; tt < TT; ++tt) {
                 const float d = s_dt[tt * CH + cl];
                 const float dx = d * s_x[tt * CH + cl];
+                float a = 0.f;
 #pragma unroll
                 for (int j = 0; j < NS; ++j) {
                     const int n = lane + j * L;
-                    if (n < N) {
-                        S[j] = fmaf(exp2f(d * A2[j]), S[j], dx * s_B[tt * N + n]);
-                        acc[tt] = fmaf(S[j], s_C[tt * N + n], acc[tt]);
-                    }
+                    S[j] = fmaf(exp2f(d * A2[j]), S[j], dx * s_B[tt * NP + n]);
+                    a = fmaf(S[j], s_C[tt * NP + n], a);
                 }
+                acc[tt] = a;
             }
-        }
 #pragma unroll
-        for (int tt = 0; tt < TT; ++tt) {
+            for (int tt = 0; tt < TT; ++tt) {
 #pragma unroll
-            for (int o = L / 2; o > 0; o >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
-            if (lane == 0 && tt < nt) s_y[tt * CH + cl] = fmaf(Dc, s_x[tt * CH + cl], acc[tt]);
+                for (int o = L / 2; o > 0; o >>= 1) acc[tt] += __shfl_xor_sync(0xffffffffu, acc[tt], o);
+                if (lane == 0) s_y[tt * CH + cl] = fmaf(Dc, s_x[tt * CH + cl], acc[tt]);
+            }
+        } else {
+            // the last tokens of a portion, a decode step: the same arithmetic, token by token
+            for (int tt = 0; tt < nt; ++tt) {
+                const float d = s_dt[tt * CH + cl];
+                const float dx = d * s_x[tt * CH + cl];
+                float a = 0.f;
+#pragma unroll
+                for (int j = 0; j < NS; ++j) {
+                    const int n = lane + j * L;
+                    S[j] = fmaf(exp2f(d * A2[j]), S[j], dx * s_B[tt * NP + n]);
+                    a = fmaf(S[j], s_C[tt * NP + n], a);
+                }
+#pragma unroll
+                for (int o = L / 2; o > 0; o >>= 1) a += __shfl_xor_sync(0xffffffffu, a, o);
+                if (lane == 0) s_y[tt * CH + cl] = fmaf(Dc, s_x[tt * CH + cl], a);
+            }
         }
         __syncthreads();
 #pragma unroll
@@ -192,7 +213,7 @@ __global__ void __launch_bounds__(NT) selective_scan_kernel(const ScanParams p) 
 template <typename TI, typename TO, int NS, int L, int TT>
 int launch(const ScanParams& p, int n_seqs, cudaStream_t s) {
     constexpr int CH = NT / L;
-    const size_t smem = (size_t)(4 * TT * CH + 2 * TT * p.N) * sizeof(float);
+    const size_t smem = (size_t)(4 * TT * CH + 2 * TT * NS * L) * sizeof(float);
     if (smem > 48 * 1024) return TL_TOO_LARGE;
     const dim3 grid((p.C + CH - 1) / CH, n_seqs);
     return (int)tl_launch(selective_scan_kernel<TI, TO, NS, L, TT>, grid, dim3(NT), smem, s, p);
