@@ -219,16 +219,42 @@ int launch(const ScanParams& p, int n_seqs, cudaStream_t s) {
     return (int)tl_launch(selective_scan_kernel<TI, TO, NS, L, TT>, grid, dim3(NT), smem, s, p);
 }
 
-// lanes per channel, state numbers per lane and tokens per chunk for a state of N numbers: four numbers a lane
-// while a warp's 32 lanes reach, more beyond (and shorter chunks, so that a chunk's inputs still fit a thread's registers)
+// lanes per channel, state numbers per lane and tokens per chunk for a state of N numbers.  Few numbers a lane mean
+// many warps, which is what hides the latencies of a walk that is serial in the tokens, and more work per token that
+// all lanes of a channel repeat: two numbers a lane up to 32 measured best (TORCHLLMS_B200_SCAN_PER_LANE = 1 or 4 asks
+// for another split, for comparisons), four where a warp's 32 lanes no longer reach, more beyond (and shorter chunks, so that a chunk's inputs still fit a thread's registers)
+static int scan_per_lane() {
+    static int v = -1;
+    if (v < 0) {
+        const char* e = getenv("TORCHLLMS_B200_SCAN_PER_LANE");
+        v = (e != nullptr && (e[0] == '1' || e[0] == '4')) ? e[0] - '0' : 2;
+    }
+    return v;
+}
+
 template <typename TI, typename TO>
 int launch_n(const ScanParams& p, int n_seqs, cudaStream_t s) {
     const int N = p.N;
+    const int per = scan_per_lane();
+    if (per == 1) {
+        if (N <= 1) return launch<TI, TO, 1, 1, 16>(p, n_seqs, s);
+        if (N <= 2) return launch<TI, TO, 1, 2, 16>(p, n_seqs, s);
+        if (N <= 4) return launch<TI, TO, 1, 4, 16>(p, n_seqs, s);
+        if (N <= 8) return launch<TI, TO, 1, 8, 16>(p, n_seqs, s);
+        if (N <= 16) return launch<TI, TO, 1, 16, 16>(p, n_seqs, s);
+        if (N <= 32) return launch<TI, TO, 1, 32, 16>(p, n_seqs, s);
+    } else if (per == 2) {
+        if (N <= 2) return launch<TI, TO, 2, 1, 16>(p, n_seqs, s);
+        if (N <= 4) return launch<TI, TO, 2, 2, 16>(p, n_seqs, s);
+        if (N <= 8) return launch<TI, TO, 2, 4, 16>(p, n_seqs, s);
+        if (N <= 16) return launch<TI, TO, 2, 8, 16>(p, n_seqs, s);
+        if (N <= 32) return launch<TI, TO, 2, 16, 16>(p, n_seqs, s);
+    }
     if (N <= 4) return launch<TI, TO, 4, 1, 16>(p, n_seqs, s);
     if (N <= 8) return launch<TI, TO, 4, 2, 16>(p, n_seqs, s);
     if (N <= 16) return launch<TI, TO, 4, 4, 16>(p, n_seqs, s);
     if (N <= 32) return launch<TI, TO, 4, 8, 16>(p, n_seqs, s);
-    if (N <= 64) return launch<TI, TO, 4, 16, 16>(p, n_seqs, s);
+    if (N <= 64) return launch<TI, TO, 2, 32, 16>(p, n_seqs, s);
     if (N <= 128) return launch<TI, TO, 4, 32, 16>(p, n_seqs, s);
     if (N <= 256) return launch<TI, TO, 8, 32, 8>(p, n_seqs, s);
     if (N <= 512) return launch<TI, TO, 16, 32, 4>(p, n_seqs, s);

@@ -5,6 +5,7 @@
     python -m torchllms_b200.kernels.microbench gemm
     python -m torchllms_b200.kernels.microbench elementwise --tokens 2048
     python -m torchllms_b200.kernels.microbench peaks
+    python -m torchllms_b200.kernels.microbench selective_scan --tokens 2048 --channels 4096 --state 16
 
 Every case is timed with CUDA events after warm-up.  Memory-bound kernels run inside a CUDA
 graph over several copies of their operands (more than the 126 MB of L2 together), so that a
@@ -166,6 +167,35 @@ def peaks(args) -> None:
     print(f"library product {m}^3 bfloat16, four hundred in a row: {us:9.1f} us  {2 * m ** 3 / us / 1e6:7.1f} TFLOP/s")
 
 
+def selective_scan(args) -> None:
+    """The selective scan alone: one prompt portion of --tokens tokens, and a decode step of 8 requests."""
+    ops = get_ops()
+    T, C, N = args.tokens, args.channels, args.state
+    torch.manual_seed(0)
+    dev, bf = "cuda", torch.bfloat16
+    for label, lens in ((f"portion of {T}", [T]), ("decode step of 8", [1] * 8)):
+        n_tok = sum(lens)
+        copies = max(1, min(8, (160 << 20) // max(1, n_tok * C * 8)))
+        sets = []
+        for _ in range(copies):
+            xz = torch.randn(n_tok, 2 * C, device=dev).to(bf)
+            dt = torch.randn(n_tok, C, device=dev).to(bf)
+            bc = torch.randn(n_tok, 2 * N, device=dev).to(bf)
+            sets.append((xz, dt, bc))
+        A = -torch.exp(torch.randn(C, N, device=dev))
+        D, bias = torch.randn(C, device=dev), torch.randn(C, device=dev)
+        state = torch.zeros(len(lens), C, N, device=dev)
+        q_start = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=dev)
+        slot = torch.arange(len(lens), dtype=torch.int32, device=dev)
+        fresh = torch.zeros(len(lens), dtype=torch.int32, device=dev)
+        calls = [(lambda xz=xz, dt=dt, bc=bc: ops.selective_scan(xz[:, :C], dt, bc[:, :N], bc[:, N:], xz[:, C:], A, D, bias, state, q_start,
+                                                                slot, fresh, n_seqs=len(lens), max_q_len=max(lens), out_dtype=bf))
+                 for xz, dt, bc in sets]
+        us = _time(_graphed(calls), 20) / copies
+        moved = n_tok * C * 2 * 4 + n_tok * N * 4 + 2 * len(lens) * C * N * 4
+        print(f"selective_scan {label}, {C} channels x {N}: {us:8.1f} us  {moved / us / 1e3:7.1f} GB/s of inputs, outputs and state")
+
+
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = parser.add_subparsers(dest="case", required=True)
@@ -183,6 +213,11 @@ def main(argv=None) -> None:
     p.set_defaults(run=gemm)
     p = sub.add_parser("peaks")
     p.set_defaults(run=peaks)
+    p = sub.add_parser("selective_scan")
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--channels", type=int, default=4096)
+    p.add_argument("--state", type=int, default=16)
+    p.set_defaults(run=selective_scan)
     p = sub.add_parser("elementwise")
     p.add_argument("--tokens", type=int, default=2048)
     p.set_defaults(run=elementwise)
